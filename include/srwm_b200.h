@@ -1,0 +1,209 @@
+/*
+ * srwm_b200.h -- C ABI of libsrwm_b200.so: the self-referential weight matrix (SRWM) and
+ * delta-rule fast-weight recurrences as hand-written sm_100a kernels.
+ *
+ * The four compute entry points replace, one for one, the four pybind functions of the
+ * reference's CUDA extensions (file:line cited at each declaration).  Everything is plain
+ * C: device pointers, sizes, element strides, a CUDA stream handle passed as void*.
+ * No buffer is owned by the library and no state is kept between calls (the calls are
+ * re-entrant; concurrent calls from several host threads are fine as long as each uses
+ * its own buffers).  Nothing is allocated on the device by these calls.
+ *
+ * Conventions
+ *   - Sequence tensors are 4-D views [N, H, L, X] (batch, head, time, feature) whose
+ *     innermost dimension is contiguous; the other three strides are given in ELEMENTS.
+ *     Each row (X elements) must start on a 16-byte boundary: base pointer and
+ *     stride*sizeof(element) are multiples of 16.  (A misaligned view returns
+ *     SRWM_B200_ERR_ALIGN; the Python layer then makes one contiguous copy.)
+ *   - State tensors are [N, H, E, X] fp32 with a dense inner [E][X] block; strides over
+ *     N and H in elements.  "matvec" is row-vector times matrix: out[m] = sum_e v[e]*W[e][m].
+ *   - io_dtype selects the element type of the streamed activations (x / out / q,k,v,beta
+ *     of the delta rule / their gradients).  State, saved activations and state gradients
+ *     are always fp32.
+ *   - Return value: 0 on success, a negative SRWM_B200_ERR_* otherwise.  Arguments are
+ *     validated before any CUDA call, so invalid calls are rejected on machines without
+ *     a GPU as well.  N*H*L == 0 is a successful no-op.
+ *   - Supported head dimensions: E in {8, 16, 32, 64} (delta rule: M == E).
+ */
+#ifndef SRWM_B200_H_
+#define SRWM_B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SRWM_B200_ABI_VERSION 1
+
+/* io_dtype */
+#define SRWM_B200_F32  0
+#define SRWM_B200_BF16 1
+
+/* error codes */
+#define SRWM_B200_OK              0
+#define SRWM_B200_ERR_NULL       -1  /* a required pointer is NULL                       */
+#define SRWM_B200_ERR_SHAPE      -2  /* negative size, or N*H exceeds the grid limit      */
+#define SRWM_B200_ERR_HEAD_DIM   -3  /* E (or M != E) not supported                       */
+#define SRWM_B200_ERR_DTYPE      -4  /* io_dtype unknown                                  */
+#define SRWM_B200_ERR_ALIGN      -5  /* a row does not start on a 16-byte boundary        */
+#define SRWM_B200_ERR_VARIANT    -6  /* tuning variant id not compiled in                 */
+#define SRWM_B200_ERR_CUDA       -7  /* CUDA runtime error; see srwm_b200_last_cuda_error */
+#define SRWM_B200_ERR_TOO_LARGE  -8  /* size beyond a fixed capacity (no-alloc entry)     */
+
+/* flags */
+#define SRWM_B200_FLAG_NO_SAVE        1u /* forward: do not write the saved-for-backward
+                                            tensors (inference; their pointers may be NULL) */
+#define SRWM_B200_FLAG_STATE_GRAD_IN  2u /* SRWM backward: grad_W_* hold dL/dW_L on entry and
+                                            are accumulated through time (stateful variant);
+                                            without it they are treated as zero on entry     */
+#define SRWM_B200_FLAG_RESTORE_STATE  4u /* SRWM backward: also write the rebuilt initial
+                                            state W_0 back into W_* (the reference leaves W_L) */
+
+typedef struct srwm_b200_seq {      /* [N,H,L,X] view, innermost contiguous */
+  void*   data;
+  int64_t stride_n, stride_h, stride_l;   /* elements */
+} srwm_b200_seq;
+
+typedef struct srwm_b200_state {    /* [N,H,E,X] fp32, inner [E][X] dense */
+  float*  data;
+  int64_t stride_n, stride_h;             /* elements */
+} srwm_b200_state;
+
+/* ------------------------------------------------------------------------------------
+ * SRWM forward.  Replaces
+ *   void self_ref_forward(x, W_y, W_q, W_k, w_b, q, k, beta, y_diff, q_diff, k_diff,
+ *                         beta_diff, output)
+ *   supervised_learning/self_ref_v0/self_ref_v0.cu:436-530 (kernel :24-432), bound at
+ *   :1344-1349; identical copy in reinforcement_learning/torchbeast/self_ref_v0/.
+ * Per step t:  [y,q~,k~,b~] = x_t.W ; q=softmax(q~), k=softmax(k~), beta=sigmoid(b~);
+ *   d_Z = (q-k).W_Z ; W_Z += k^T (beta_Z d_Z)   for Z in {y,q,k,b}; out_t = y (pre-update).
+ * The final state is written back IN PLACE into W_y, W_q, W_k, w_b (callers rely on it).
+ * Outputs are plain stores: no zero-filling by the caller is needed.
+ * ---------------------------------------------------------------------------------- */
+typedef struct srwm_b200_srwm_fwd_args {
+  int32_t N, H, L, E;
+  int32_t io_dtype;
+  uint32_t flags;
+  int32_t variant;                  /* 0 = default kernel configuration */
+  int32_t reserved;
+  srwm_b200_seq   x;                /* in  [N,H,L,E] io_dtype */
+  srwm_b200_state W_y, W_q, W_k;    /* in/out [N,H,E,E] */
+  srwm_b200_state w_b;              /* in/out [N,H,E,4] */
+  srwm_b200_seq   out;              /* out [N,H,L,E] io_dtype */
+  srwm_b200_seq   q, k;             /* saved [N,H,L,E] fp32 (softmax outputs) */
+  srwm_b200_seq   beta;             /* saved [N,H,L,4] fp32 (post-sigmoid) */
+  srwm_b200_seq   y_diff, q_diff, k_diff;  /* saved [N,H,L,E] fp32: (q-k).W_Z */
+  srwm_b200_seq   beta_diff;        /* saved [N,H,L,4] fp32 */
+} srwm_b200_srwm_fwd_args;
+
+int srwm_b200_srwm_forward(const srwm_b200_srwm_fwd_args* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------
+ * SRWM backward.  Replaces
+ *   void self_ref_backward(x, q, k, beta, y_diff, q_diff, k_diff, beta_diff, grad_out,
+ *                          Wy, Wq, Wk, wb, grad_x, grad_Wy, grad_Wq, grad_Wk, grad_wb)
+ *   supervised_learning/self_ref_v0/self_ref_v0.cu:1238-1341 (kernel :534-1234), bound at
+ *   :1350-1355.
+ * Reverse-time pass that rebuilds W_{t-1} from W_t by undoing the rank-1 update; W_* must
+ * hold the FINAL state left by the forward.  grad_W_* receive dL/dW_0 (plain stores).
+ * Unlike the reference the whole sequence is one launch, so L is not limited by a
+ * shared-memory time chunk.
+ * ---------------------------------------------------------------------------------- */
+typedef struct srwm_b200_srwm_bwd_args {
+  int32_t N, H, L, E;
+  int32_t io_dtype;
+  uint32_t flags;
+  int32_t variant;
+  int32_t reserved;
+  srwm_b200_seq   x;                /* in  [N,H,L,E] io_dtype */
+  srwm_b200_seq   q, k;             /* in  saved fp32 */
+  srwm_b200_seq   beta;             /* in  saved fp32 [N,H,L,4] */
+  srwm_b200_seq   y_diff, q_diff, k_diff;
+  srwm_b200_seq   beta_diff;
+  srwm_b200_seq   grad_out;         /* in  [N,H,L,E] io_dtype */
+  srwm_b200_state W_y, W_q, W_k, w_b;             /* in (W_L); out W_0 with RESTORE_STATE */
+  srwm_b200_seq   grad_x;           /* out [N,H,L,E] io_dtype */
+  srwm_b200_state grad_W_y, grad_W_q, grad_W_k, grad_w_b;   /* (in)/out fp32 */
+} srwm_b200_srwm_bwd_args;
+
+int srwm_b200_srwm_backward(const srwm_b200_srwm_bwd_args* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------
+ * Delta-rule forward.  Replaces
+ *   void fast_weight_forward(Q, K, V, beta, v_old, v_insert, kv, out)
+ *   supervised_learning/fast_weight/fast_weight_cuda.cu:182-240 (kernel :17-178), bound at
+ *   :667-672; identical copy in reinforcement_learning/torchbeast/fast_weight/.
+ * Per step:  v_old = k.W ; ins = beta (v - v_old) ; W += k^T ins ; out = q.W (post-update).
+ * Q and K are used as given (already normalised by the caller), beta is post-sigmoid.
+ * The final W is written back in place.
+ * ---------------------------------------------------------------------------------- */
+typedef struct srwm_b200_delta_fwd_args {
+  int32_t N, H, L, E, M;
+  int32_t io_dtype;
+  uint32_t flags;
+  int32_t variant;
+  srwm_b200_seq   Q, K;             /* in [N,H,L,E] io_dtype */
+  srwm_b200_seq   V;                /* in [N,H,L,M] io_dtype */
+  srwm_b200_seq   beta;             /* in [N,H,L,1] io_dtype (any stride; no alignment rule) */
+  srwm_b200_state W;                /* in/out [N,H,E,M] */
+  srwm_b200_seq   out;              /* out [N,H,L,M] io_dtype */
+  srwm_b200_seq   v_old, v_insert;  /* saved [N,H,L,M] fp32 */
+} srwm_b200_delta_fwd_args;
+
+int srwm_b200_delta_forward(const srwm_b200_delta_fwd_args* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------
+ * Delta-rule backward.  Replaces
+ *   void fast_weight_backward(Q, K, V, beta, v_old, v_insert, grad_out, fw_mem,
+ *                             grad_q, grad_k, grad_v, grad_betas)
+ *   supervised_learning/fast_weight/fast_weight_cuda.cu:564-664 (kernels :244-393 and
+ *   :397-560), bound at :673-678.
+ * One reverse-time pass (the reference uses two and a [N,H,L,M] temporary).  W holds W_L
+ * on entry and the rebuilt W_0 on exit, as in the reference (:391).  grad_W0 is optional
+ * (NULL data = not wanted; the reference's autograd function returns None for it).
+ * ---------------------------------------------------------------------------------- */
+typedef struct srwm_b200_delta_bwd_args {
+  int32_t N, H, L, E, M;
+  int32_t io_dtype;
+  uint32_t flags;
+  int32_t variant;
+  srwm_b200_seq   Q, K, V, beta;    /* in, io_dtype */
+  srwm_b200_seq   v_old, v_insert;  /* in, saved fp32 */
+  srwm_b200_seq   grad_out;         /* in [N,H,L,M] io_dtype */
+  srwm_b200_state W;                /* in W_L / out W_0 */
+  srwm_b200_seq   grad_Q, grad_K;   /* out [N,H,L,E] io_dtype */
+  srwm_b200_seq   grad_V;           /* out [N,H,L,M] io_dtype */
+  srwm_b200_seq   grad_beta;        /* out [N,H,L,1] io_dtype (any stride) */
+  srwm_b200_state grad_W0;          /* optional out [N,H,E,M] fp32 */
+} srwm_b200_delta_bwd_args;
+
+int srwm_b200_delta_backward(const srwm_b200_delta_bwd_args* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------
+ * Batch reduction of per-sample state gradients into the slow-weight gradient:
+ *   dst[i] (+)= sum_n src[n*stride_n + i],  i < count   (fp32, deterministic order).
+ * This is the backward of the callers' `W.repeat(bsz, 1, 1, 1)`
+ * (supervised_learning/layer.py:174-177); dst may point into a flat all-reduce bucket.
+ * accumulate != 0 adds to dst instead of overwriting it.
+ * ---------------------------------------------------------------------------------- */
+int srwm_b200_reduce_batch(const float* src, int64_t stride_n, int32_t N, int64_t count,
+                           float* dst, int32_t accumulate, void* cuda_stream);
+
+/* ---- queries (no CUDA call is made by these) ---- */
+int         srwm_b200_abi_version(void);
+int         srwm_b200_head_dim_supported(int32_t E);           /* 1 / 0 */
+int         srwm_b200_num_variants(int32_t op, int32_t E);     /* op: 0 srwm_fwd 1 srwm_bwd
+                                                                  2 delta_fwd 3 delta_bwd */
+const char* srwm_b200_strerror(int code);
+int         srwm_b200_last_cuda_error(void);   /* cudaError_t of the last failed call of the
+                                                  calling thread, 0 if none */
+/* Describes the kernel configuration a call would use (threads per sequence, rows per
+ * thread, time-chunk length, dynamic shared memory bytes): writes "P R T smem" into out. */
+int         srwm_b200_describe(int32_t op, int32_t E, int32_t io_dtype, int32_t variant,
+                               int32_t out[4]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* SRWM_B200_H_ */

@@ -1,0 +1,308 @@
+// C ABI of libsrwm_b200.so (see include/srwm_b200.h): argument validation, conversion of
+// element strides to the kernels' byte strides, dispatch to the compiled configuration.
+// All validation happens before the first CUDA call.
+#include "srwm_b200.h"
+
+#include "configs.h"
+#include "launch.h"
+
+namespace {
+
+thread_local int g_last_cuda_error = 0;
+
+inline int esize(int dtype) { return dtype == SRWM_B200_BF16 ? 2 : 4; }
+
+inline bool head_dim_ok(int E) { return E == 8 || E == 16 || E == 32 || E == 64; }
+
+// Every row of a streamed tensor must start on a 16-byte boundary.
+inline bool seq_aligned(const srwm_b200_seq& t, int es) {
+  return ((uintptr_t)t.data % 16 == 0) && ((t.stride_n * es) % 16 == 0) && ((t.stride_h * es) % 16 == 0) &&
+         ((t.stride_l * es) % 16 == 0);
+}
+inline bool state_aligned(const srwm_b200_state& t) {
+  return ((uintptr_t)t.data % 16 == 0) && ((t.stride_n * 4) % 16 == 0) && ((t.stride_h * 4) % 16 == 0);
+}
+inline srwm::SeqView view(const srwm_b200_seq& t, int es) {
+  srwm::SeqView v;
+  v.base = reinterpret_cast<char*>(t.data);
+  v.sn = t.stride_n * es;
+  v.sh = t.stride_h * es;
+  v.sl = t.stride_l * es;
+  return v;
+}
+inline srwm::StateView view(const srwm_b200_state& t) {
+  srwm::StateView v;
+  v.base = t.data;
+  v.sn = t.stride_n;
+  v.sh = t.stride_h;
+  return v;
+}
+
+inline int check_dims(int N, int H, int L, long long* grid) {
+  if (N < 0 || H < 0 || L < 0) return SRWM_B200_ERR_SHAPE;
+  const long long g = (long long)N * H;
+  if (g > 0x7fffffffLL) return SRWM_B200_ERR_SHAPE;
+  *grid = g;
+  return 0;
+}
+
+inline int finish(int rc, int cuda_err) {
+  if (rc == -7) {
+    g_last_cuda_error = cuda_err;
+    return SRWM_B200_ERR_CUDA;
+  }
+  if (rc == -6) return SRWM_B200_ERR_VARIANT;
+  if (rc == -3) return SRWM_B200_ERR_HEAD_DIM;
+  return rc;
+}
+
+}  // namespace
+
+extern "C" {
+
+int srwm_b200_abi_version(void) { return SRWM_B200_ABI_VERSION; }
+
+int srwm_b200_head_dim_supported(int32_t E) { return head_dim_ok(E) ? 1 : 0; }
+
+int srwm_b200_last_cuda_error(void) { return g_last_cuda_error; }
+
+const char* srwm_b200_strerror(int code) {
+  switch (code) {
+    case SRWM_B200_OK: return "ok";
+    case SRWM_B200_ERR_NULL: return "a required pointer is NULL";
+    case SRWM_B200_ERR_SHAPE: return "invalid shape (negative size or N*H too large)";
+    case SRWM_B200_ERR_HEAD_DIM: return "head dimension not supported (E must be 8, 16, 32 or 64; delta rule needs M == E)";
+    case SRWM_B200_ERR_DTYPE: return "unknown io_dtype";
+    case SRWM_B200_ERR_ALIGN: return "a tensor row does not start on a 16-byte boundary";
+    case SRWM_B200_ERR_VARIANT: return "kernel variant not compiled in";
+    case SRWM_B200_ERR_CUDA: return "CUDA runtime error (see srwm_b200_last_cuda_error)";
+    case SRWM_B200_ERR_TOO_LARGE: return "size exceeds the fixed capacity of this entry point";
+    default: return "unknown error code";
+  }
+}
+
+int srwm_b200_describe(int32_t op, int32_t E, int32_t io_dtype, int32_t variant, int32_t out[4]) {
+  if (!out) return SRWM_B200_ERR_NULL;
+  if (io_dtype != SRWM_B200_F32 && io_dtype != SRWM_B200_BF16) return SRWM_B200_ERR_DTYPE;
+  srwm::KernelInfo info = {0, 0, 0, 0};
+  int ce = 0, rc;
+  const bool bf = io_dtype == SRWM_B200_BF16;
+  switch (op) {
+    case srwm::OP_SRWM_FWD: {
+      srwm::SrwmFwdParams p = {};
+      rc = bf ? srwm::dispatch_srwm_fwd_bf16(E, variant, p, 0, 0, &info, 1, &ce)
+              : srwm::dispatch_srwm_fwd_f32(E, variant, p, 0, 0, &info, 1, &ce);
+      break;
+    }
+    case srwm::OP_SRWM_BWD: {
+      srwm::SrwmBwdParams p = {};
+      rc = bf ? srwm::dispatch_srwm_bwd_bf16(E, variant, p, 0, 0, &info, 1, &ce)
+              : srwm::dispatch_srwm_bwd_f32(E, variant, p, 0, 0, &info, 1, &ce);
+      break;
+    }
+    case srwm::OP_DELTA_FWD: {
+      srwm::DeltaFwdParams p = {};
+      rc = bf ? srwm::dispatch_delta_fwd_bf16(E, variant, p, 0, 0, &info, 1, &ce)
+              : srwm::dispatch_delta_fwd_f32(E, variant, p, 0, 0, &info, 1, &ce);
+      break;
+    }
+    case srwm::OP_DELTA_BWD: {
+      srwm::DeltaBwdParams p = {};
+      rc = bf ? srwm::dispatch_delta_bwd_bf16(E, variant, p, 0, 0, &info, 1, &ce)
+              : srwm::dispatch_delta_bwd_f32(E, variant, p, 0, 0, &info, 1, &ce);
+      break;
+    }
+    default:
+      return SRWM_B200_ERR_SHAPE;
+  }
+  if (rc != 0) return finish(rc, ce);
+  out[0] = info.P; out[1] = info.R; out[2] = info.T; out[3] = info.smem;
+  return 0;
+}
+
+int srwm_b200_num_variants(int32_t op, int32_t E) {
+  int n = 0;
+  int32_t tmp[4];
+  while (n < 64 && srwm_b200_describe(op, E, SRWM_B200_F32, n, tmp) == 0) ++n;
+  return n;
+}
+
+// ---------------------------------------------------------------------------------------
+int srwm_b200_srwm_forward(const srwm_b200_srwm_fwd_args* a, void* stream) {
+  if (!a) return SRWM_B200_ERR_NULL;
+  long long grid;
+  if (int rc = check_dims(a->N, a->H, a->L, &grid)) return rc;
+  if (!head_dim_ok(a->E)) return SRWM_B200_ERR_HEAD_DIM;
+  if (a->io_dtype != SRWM_B200_F32 && a->io_dtype != SRWM_B200_BF16) return SRWM_B200_ERR_DTYPE;
+  if (grid == 0 || a->L == 0) return 0;
+  const bool save = !(a->flags & SRWM_B200_FLAG_NO_SAVE);
+  if (!a->x.data || !a->out.data || !a->W_y.data || !a->W_q.data || !a->W_k.data || !a->w_b.data)
+    return SRWM_B200_ERR_NULL;
+  if (save && (!a->q.data || !a->k.data || !a->beta.data || !a->y_diff.data || !a->q_diff.data ||
+               !a->k_diff.data || !a->beta_diff.data))
+    return SRWM_B200_ERR_NULL;
+  const int es = esize(a->io_dtype);
+  bool ok = seq_aligned(a->x, es) && seq_aligned(a->out, es) && state_aligned(a->W_y) && state_aligned(a->W_q) &&
+            state_aligned(a->W_k) && state_aligned(a->w_b);
+  if (save)
+    ok = ok && seq_aligned(a->q, 4) && seq_aligned(a->k, 4) && seq_aligned(a->beta, 4) && seq_aligned(a->y_diff, 4) &&
+         seq_aligned(a->q_diff, 4) && seq_aligned(a->k_diff, 4) && seq_aligned(a->beta_diff, 4);
+  if (!ok) return SRWM_B200_ERR_ALIGN;
+
+  srwm::SrwmFwdParams p;
+  p.N = a->N; p.H = a->H; p.L = a->L; p.flags = a->flags;
+  p.x = view(a->x, es); p.out = view(a->out, es);
+  p.q = view(a->q, 4); p.k = view(a->k, 4); p.beta = view(a->beta, 4);
+  p.yd = view(a->y_diff, 4); p.qd = view(a->q_diff, 4); p.kd = view(a->k_diff, 4); p.bd = view(a->beta_diff, 4);
+  p.Wy = view(a->W_y); p.Wq = view(a->W_q); p.Wk = view(a->W_k); p.wb = view(a->w_b);
+  int ce = 0;
+  const int rc = a->io_dtype == SRWM_B200_BF16
+                     ? srwm::dispatch_srwm_fwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
+                     : srwm::dispatch_srwm_fwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+  return finish(rc, ce);
+}
+
+int srwm_b200_srwm_backward(const srwm_b200_srwm_bwd_args* a, void* stream) {
+  if (!a) return SRWM_B200_ERR_NULL;
+  long long grid;
+  if (int rc = check_dims(a->N, a->H, a->L, &grid)) return rc;
+  if (!head_dim_ok(a->E)) return SRWM_B200_ERR_HEAD_DIM;
+  if (a->io_dtype != SRWM_B200_F32 && a->io_dtype != SRWM_B200_BF16) return SRWM_B200_ERR_DTYPE;
+  if (grid == 0) return 0;
+  if (!a->W_y.data || !a->W_q.data || !a->W_k.data || !a->w_b.data || !a->grad_W_y.data || !a->grad_W_q.data ||
+      !a->grad_W_k.data || !a->grad_w_b.data)
+    return SRWM_B200_ERR_NULL;
+  if (a->L > 0 && (!a->x.data || !a->q.data || !a->k.data || !a->beta.data || !a->y_diff.data || !a->q_diff.data ||
+                   !a->k_diff.data || !a->beta_diff.data || !a->grad_out.data || !a->grad_x.data))
+    return SRWM_B200_ERR_NULL;
+  const int es = esize(a->io_dtype);
+  bool ok = state_aligned(a->W_y) && state_aligned(a->W_q) && state_aligned(a->W_k) && state_aligned(a->w_b) &&
+            state_aligned(a->grad_W_y) && state_aligned(a->grad_W_q) && state_aligned(a->grad_W_k) &&
+            state_aligned(a->grad_w_b);
+  if (a->L > 0)
+    ok = ok && seq_aligned(a->x, es) && seq_aligned(a->grad_out, es) && seq_aligned(a->grad_x, es) &&
+         seq_aligned(a->q, 4) && seq_aligned(a->k, 4) && seq_aligned(a->beta, 4) && seq_aligned(a->y_diff, 4) &&
+         seq_aligned(a->q_diff, 4) && seq_aligned(a->k_diff, 4) && seq_aligned(a->beta_diff, 4);
+  if (!ok) return SRWM_B200_ERR_ALIGN;
+
+  srwm::SrwmBwdParams p;
+  p.N = a->N; p.H = a->H; p.L = a->L; p.flags = a->flags;
+  p.x = view(a->x, es); p.gout = view(a->grad_out, es); p.gx = view(a->grad_x, es);
+  p.q = view(a->q, 4); p.k = view(a->k, 4); p.beta = view(a->beta, 4);
+  p.yd = view(a->y_diff, 4); p.qd = view(a->q_diff, 4); p.kd = view(a->k_diff, 4); p.bd = view(a->beta_diff, 4);
+  p.Wy = view(a->W_y); p.Wq = view(a->W_q); p.Wk = view(a->W_k); p.wb = view(a->w_b);
+  p.gWy = view(a->grad_W_y); p.gWq = view(a->grad_W_q); p.gWk = view(a->grad_W_k); p.gwb = view(a->grad_w_b);
+  int ce = 0;
+  const int rc = a->io_dtype == SRWM_B200_BF16
+                     ? srwm::dispatch_srwm_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
+                     : srwm::dispatch_srwm_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+  return finish(rc, ce);
+}
+
+int srwm_b200_delta_forward(const srwm_b200_delta_fwd_args* a, void* stream) {
+  if (!a) return SRWM_B200_ERR_NULL;
+  long long grid;
+  if (int rc = check_dims(a->N, a->H, a->L, &grid)) return rc;
+  if (!head_dim_ok(a->E) || a->M != a->E) return SRWM_B200_ERR_HEAD_DIM;
+  if (a->io_dtype != SRWM_B200_F32 && a->io_dtype != SRWM_B200_BF16) return SRWM_B200_ERR_DTYPE;
+  if (grid == 0 || a->L == 0) return 0;
+  const bool save = !(a->flags & SRWM_B200_FLAG_NO_SAVE);
+  if (!a->Q.data || !a->K.data || !a->V.data || !a->beta.data || !a->W.data || !a->out.data) return SRWM_B200_ERR_NULL;
+  if (save && (!a->v_old.data || !a->v_insert.data)) return SRWM_B200_ERR_NULL;
+  const int es = esize(a->io_dtype);
+  bool ok = seq_aligned(a->Q, es) && seq_aligned(a->K, es) && seq_aligned(a->V, es) && seq_aligned(a->out, es) &&
+            state_aligned(a->W) && ((uintptr_t)a->beta.data % es == 0);
+  if (save) ok = ok && seq_aligned(a->v_old, 4) && seq_aligned(a->v_insert, 4);
+  if (!ok) return SRWM_B200_ERR_ALIGN;
+
+  srwm::DeltaFwdParams p;
+  p.N = a->N; p.H = a->H; p.L = a->L; p.flags = a->flags;
+  p.Q = view(a->Q, es); p.K = view(a->K, es); p.V = view(a->V, es); p.beta = view(a->beta, es);
+  p.out = view(a->out, es); p.v_old = view(a->v_old, 4); p.v_ins = view(a->v_insert, 4);
+  p.W = view(a->W);
+  int ce = 0;
+  const int rc = a->io_dtype == SRWM_B200_BF16
+                     ? srwm::dispatch_delta_fwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
+                     : srwm::dispatch_delta_fwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+  return finish(rc, ce);
+}
+
+int srwm_b200_delta_backward(const srwm_b200_delta_bwd_args* a, void* stream) {
+  if (!a) return SRWM_B200_ERR_NULL;
+  long long grid;
+  if (int rc = check_dims(a->N, a->H, a->L, &grid)) return rc;
+  if (!head_dim_ok(a->E) || a->M != a->E) return SRWM_B200_ERR_HEAD_DIM;
+  if (a->io_dtype != SRWM_B200_F32 && a->io_dtype != SRWM_B200_BF16) return SRWM_B200_ERR_DTYPE;
+  if (grid == 0) return 0;
+  if (!a->W.data) return SRWM_B200_ERR_NULL;
+  if (a->L > 0 && (!a->Q.data || !a->K.data || !a->V.data || !a->beta.data || !a->v_old.data || !a->v_insert.data ||
+                   !a->grad_out.data || !a->grad_Q.data || !a->grad_K.data || !a->grad_V.data || !a->grad_beta.data))
+    return SRWM_B200_ERR_NULL;
+  const int es = esize(a->io_dtype);
+  bool ok = state_aligned(a->W) && (a->grad_W0.data == nullptr || state_aligned(a->grad_W0));
+  if (a->L > 0)
+    ok = ok && seq_aligned(a->Q, es) && seq_aligned(a->K, es) && seq_aligned(a->V, es) && seq_aligned(a->grad_out, es) &&
+         seq_aligned(a->grad_Q, es) && seq_aligned(a->grad_K, es) && seq_aligned(a->grad_V, es) &&
+         seq_aligned(a->v_old, 4) && seq_aligned(a->v_insert, 4) && ((uintptr_t)a->beta.data % es == 0) &&
+         ((uintptr_t)a->grad_beta.data % es == 0);
+  if (!ok) return SRWM_B200_ERR_ALIGN;
+
+  srwm::DeltaBwdParams p;
+  p.N = a->N; p.H = a->H; p.L = a->L; p.flags = a->flags;
+  p.Q = view(a->Q, es); p.K = view(a->K, es); p.V = view(a->V, es); p.beta = view(a->beta, es);
+  p.v_old = view(a->v_old, 4); p.v_ins = view(a->v_insert, 4); p.gout = view(a->grad_out, es);
+  p.gQ = view(a->grad_Q, es); p.gK = view(a->grad_K, es); p.gV = view(a->grad_V, es); p.gbeta = view(a->grad_beta, es);
+  p.W = view(a->W); p.gW0 = view(a->grad_W0);
+  int ce = 0;
+  const int rc = a->io_dtype == SRWM_B200_BF16
+                     ? srwm::dispatch_delta_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
+                     : srwm::dispatch_delta_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+  return finish(rc, ce);
+}
+
+}  // extern "C"
+
+// ---------------------------------------------------------------------------------------
+// Batch reduction: dst[i] (+)= sum_n src[n*stride_n + i].  One thread per 4 outputs, the
+// batch walked in a fixed order (deterministic); reads are 16-byte and coalesced.
+// ---------------------------------------------------------------------------------------
+namespace {
+__global__ void __launch_bounds__(256) reduce_batch_kernel(const float* __restrict__ src, long long stride_n, int N,
+                                                           long long count, float* __restrict__ dst, int accumulate) {
+  const long long i4 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long i = i4 * 4;
+  if (i >= count) return;
+  if (i + 4 <= count) {
+    float4 acc = accumulate ? *reinterpret_cast<const float4*>(dst + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int n = 0; n < N; ++n) {
+      const float4 v = *reinterpret_cast<const float4*>(src + (long long)n * stride_n + i);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    *reinterpret_cast<float4*>(dst + i) = acc;
+  } else {
+    for (long long j = i; j < count; ++j) {
+      float acc = accumulate ? dst[j] : 0.f;
+      for (int n = 0; n < N; ++n) acc += src[(long long)n * stride_n + j];
+      dst[j] = acc;
+    }
+  }
+}
+}  // namespace
+
+extern "C" int srwm_b200_reduce_batch(const float* src, int64_t stride_n, int32_t N, int64_t count, float* dst,
+                                      int32_t accumulate, void* stream) {
+  if (N < 0 || count < 0) return SRWM_B200_ERR_SHAPE;
+  if (count == 0) return 0;
+  if (!dst || (N > 0 && !src)) return SRWM_B200_ERR_NULL;
+  if ((uintptr_t)src % 16 || (uintptr_t)dst % 16 || (stride_n * 4) % 16) return SRWM_B200_ERR_ALIGN;
+  const long long n4 = (count + 3) / 4;
+  const long long blocks = (n4 + 255) / 256;
+  if (blocks > 0x7fffffffLL) return SRWM_B200_ERR_SHAPE;
+  reduce_batch_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(src, stride_n, N, count, dst, accumulate);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    g_last_cuda_error = (int)e;
+    return SRWM_B200_ERR_CUDA;
+  }
+  return 0;
+}

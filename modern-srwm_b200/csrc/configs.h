@@ -1,0 +1,60 @@
+// Compiled kernel configurations: X(E, variant, P, R, T, PK, MINB)
+//   E      head dimension            P     threads per sequence (= CTA size)
+//   R      state rows per thread     T     time steps staged per chunk
+//   PK     packed fma.rn.f32x2 (1) or scalar fma (0)
+//   MINB   CTAs per SM the register allocation is bounded for (__launch_bounds__)
+// Variant 0 is what the library uses by default; the others exist so that alternative
+// tilings can be timed against each other through the same ABI.
+#pragma once
+
+#define SRWM_FWD_CONFIGS(X)      \
+  X(8, 0, 32, 2, 16, true, 8)    \
+  X(16, 0, 32, 4, 16, true, 8)   \
+  X(16, 1, 32, 2, 16, true, 8)   \
+  X(32, 0, 64, 8, 16, true, 6)   \
+  X(32, 1, 32, 8, 16, true, 8)   \
+  X(32, 2, 64, 4, 16, true, 6)   \
+  X(32, 3, 128, 8, 16, true, 4)  \
+  X(64, 0, 128, 8, 16, true, 3)  \
+  X(64, 1, 128, 16, 16, true, 3) \
+  X(64, 2, 256, 8, 16, true, 2)  \
+  X(64, 3, 128, 8, 16, false, 3) \
+  X(64, 4, 256, 16, 16, true, 2)
+
+#define SRWM_BWD_CONFIGS(X)      \
+  X(8, 0, 32, 2, 16, true, 8)    \
+  X(16, 0, 32, 4, 16, true, 8)   \
+  X(16, 1, 32, 2, 16, true, 8)   \
+  X(32, 0, 64, 8, 16, true, 6)   \
+  X(32, 1, 64, 4, 16, true, 6)   \
+  X(32, 2, 32, 8, 16, true, 8)   \
+  X(32, 3, 128, 8, 16, true, 4)  \
+  X(64, 0, 128, 8, 16, true, 2)  \
+  X(64, 1, 256, 8, 16, true, 1)  \
+  X(64, 2, 256, 4, 16, true, 1)  \
+  X(64, 3, 128, 8, 16, false, 2) \
+  X(64, 4, 128, 16, 16, true, 2) \
+  X(64, 5, 512, 8, 8, true, 1)
+
+#define DELTA_FWD_CONFIGS(X)     \
+  X(8, 0, 32, 2, 16, true, 8)    \
+  X(16, 0, 32, 4, 16, true, 8)   \
+  X(32, 0, 32, 8, 16, true, 12)  \
+  X(32, 1, 64, 8, 16, true, 8)   \
+  X(64, 0, 64, 16, 8, true, 8)   \
+  X(64, 1, 64, 32, 8, true, 8)   \
+  X(64, 2, 64, 64, 8, true, 8)   \
+  X(64, 3, 128, 16, 8, true, 6)  \
+  X(64, 4, 32, 16, 8, true, 10)  \
+  X(64, 5, 64, 16, 8, false, 8)
+
+#define DELTA_BWD_CONFIGS(X)     \
+  X(8, 0, 32, 2, 16, true, 8)    \
+  X(16, 0, 32, 4, 16, true, 8)   \
+  X(32, 0, 32, 8, 16, true, 10)  \
+  X(32, 1, 64, 8, 16, true, 8)   \
+  X(64, 0, 64, 16, 8, true, 4)   \
+  X(64, 1, 128, 8, 8, true, 4)   \
+  X(64, 2, 128, 16, 8, true, 4)  \
+  X(64, 3, 64, 8, 8, true, 4)    \
+  X(64, 4, 64, 16, 8, false, 4)

@@ -1,0 +1,416 @@
+// Delta-rule fast-weight recurrence, forward and single-pass backward, for sm_100a.
+//
+// Semantics follow the reference's ground-truth loop
+// (supervised_learning/fast_weight/__init__.py:186-191) and what its kernels save / leave
+// behind (supervised_learning/fast_weight/fast_weight_cuda.cu:101-169, :391):
+//   v_old = k.W ; ins = beta*(v - v_old) ; W += k^T ins ; out = q.W   (post-update W)
+// The state W[E][M] (M == E) of one (batch, head) sequence is a register tile spread over
+// the P threads of one CTA (see common.cuh); there is no block-wide barrier inside the
+// time loop of either kernel -- only warp shuffles.
+#pragma once
+#include "common.cuh"
+
+namespace srwm {
+
+struct DeltaFwdParams {
+  int N, H, L;
+  unsigned flags;
+  SeqView Q, K, V, beta, out, v_old, v_ins;
+  StateView W;
+};
+
+struct DeltaBwdParams {
+  int N, H, L;
+  unsigned flags;
+  SeqView Q, K, V, beta, v_old, v_ins, gout, gQ, gK, gV, gbeta;
+  StateView W, gW0;
+};
+
+template <typename TIO, int E, int T>
+struct DeltaFwdSmem {
+  static constexpr int ROW_IO = E * (int)sizeof(TIO);
+  static constexpr int ROW_F = E * 4;
+  static constexpr int BETA_BYTES = ((T * 4 + 15) / 16) * 16;
+  static constexpr int IN_BYTES = 3 * T * ROW_IO + BETA_BYTES;   // q,k,v,beta of one buffer
+  static constexpr int OUT_BYTES = T * ROW_IO + 2 * T * ROW_F;   // out, v_old, v_ins
+  static constexpr int TOTAL = 2 * IN_BYTES + OUT_BYTES;
+};
+
+template <typename TIO, int E, int P, int R, int T, bool PK, int MINB>
+__global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams p) {
+  using TL = Tiling<E, P, R>;
+  using SM = DeltaFwdSmem<TIO, E, T>;
+  constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2;
+  const int tid = threadIdx.x;
+  const int rg = tid % NRG, cg = tid / NRG;
+  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
+  const bool save = !(p.flags & 1u);
+
+  extern __shared__ __align__(16) unsigned char smem[];
+  unsigned char* s_out = smem + 2 * SM::IN_BYTES;
+  TIO* so = reinterpret_cast<TIO*>(s_out);
+  float* svold = reinterpret_cast<float*>(s_out + T * SM::ROW_IO);
+  float* svins = svold + T * E;
+
+  // state tile
+  u64 W[R2][C];
+  float* Wg = p.W.mat(n, h);
+#pragma unroll
+  for (int i2 = 0; i2 < R2; ++i2) {
+    float a[C], b[C];
+    ld_vec<C>(Wg + (rg * R + 2 * i2) * E + cg * C, a);
+    ld_vec<C>(Wg + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+#pragma unroll
+    for (int j = 0; j < C; ++j) W[i2][j] = pack2(a[j], b[j]);
+  }
+
+  const int L = p.L;
+  const int nchunks = (L + T - 1) / T;
+  auto in_buf = [&](int b) { return smem + b * SM::IN_BYTES; };
+  auto stage_chunk = [&](int c) {
+    const int t0 = c * T, nt = min(T, L - t0);
+    unsigned char* ib = in_buf(c & 1);
+    stage_rows<SM::ROW_IO, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, tid);
+    stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.K.row(n, h, t0), p.K.sl, nt, tid);
+    stage_rows<SM::ROW_IO, P>(ib + 2 * T * SM::ROW_IO, p.V.row(n, h, t0), p.V.sl, nt, tid);
+  };
+  auto beta_ld = [&](int c, int i) -> float {   // i-th step of chunk c (plain load: rows are 1 element)
+    return to_f32(*reinterpret_cast<const TIO*>(p.beta.row(n, h, c * T + i)));
+  };
+  auto beta_buf = [&](int b) { return reinterpret_cast<float*>(in_buf(b) + 3 * T * SM::ROW_IO); };
+
+  stage_chunk(0);
+  cp_async_commit();
+  for (int i = tid; i < min(T, L); i += P) beta_buf(0)[i] = beta_ld(0, i);
+
+  for (int c = 0; c < nchunks; ++c) {
+    const int t0 = c * T, nt = min(T, L - t0);
+    const bool has_next = (c + 1 < nchunks);
+    const int nt_next = has_next ? min(T, L - (t0 + T)) : 0;
+    float bnext[(T + P - 1) / P];
+    if (has_next) {
+      stage_chunk(c + 1);
+#pragma unroll
+      for (int u = 0; u < (T + P - 1) / P; ++u) {
+        const int i = tid + u * P;
+        bnext[u] = (i < nt_next) ? beta_ld(c + 1, i) : 0.f;
+      }
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    const unsigned char* ib = in_buf(c & 1);
+    const TIO* sq = reinterpret_cast<const TIO*>(ib);
+    const TIO* sk = reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO);
+    const TIO* sv = reinterpret_cast<const TIO*>(ib + 2 * T * SM::ROW_IO);
+    const float* sb = beta_buf(c & 1);
+
+    for (int t = 0; t < nt; ++t) {
+      float kr[R], qr[R], vc[C];
+      ld_vec<R>(sk + t * E + rg * R, kr);
+      ld_vec<R>(sq + t * E + rg * R, qr);
+      ld_vec<C>(sv + t * E + cg * C, vc);
+      const float bt = sb[t];
+
+      u64 av[C], ao[C];
+#pragma unroll
+      for (int j = 0; j < C; ++j) { av[j] = 0ull; ao[j] = 0ull; }
+      float qk = 0.f;
+      u64 k2[R2];
+#pragma unroll
+      for (int i2 = 0; i2 < R2; ++i2) {
+        k2[i2] = pack2(kr[2 * i2], kr[2 * i2 + 1]);
+        const u64 q2 = pack2(qr[2 * i2], qr[2 * i2 + 1]);
+        qk = fmaf(kr[2 * i2], qr[2 * i2], qk);
+        qk = fmaf(kr[2 * i2 + 1], qr[2 * i2 + 1], qk);
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+          av[j] = fma2<PK>(k2[i2], W[i2][j], av[j]);
+          ao[j] = fma2<PK>(q2, W[i2][j], ao[j]);
+        }
+      }
+      float vold[C], o[C], ins[C];
+      qk = allreduce_rows<NRG>(qk);
+#pragma unroll
+      for (int j = 0; j < C; ++j) {
+        vold[j] = allreduce_rows<NRG>(hsum2(av[j]));
+        o[j] = allreduce_rows<NRG>(hsum2(ao[j]));
+        ins[j] = bt * (vc[j] - vold[j]);
+        o[j] = fmaf(qk, ins[j], o[j]);   // q.(W + k^T ins) = q.W + (q.k) ins
+      }
+#pragma unroll
+      for (int j = 0; j < C; ++j) {
+        const u64 i2v = dup2(ins[j]);
+#pragma unroll
+        for (int i2 = 0; i2 < R2; ++i2) W[i2][j] = fma2<PK>(k2[i2], i2v, W[i2][j]);
+      }
+      if (rg == 0) {
+        st_vec<C>(so + t * E + cg * C, o);
+        if (save) {
+          st_vec<C>(svold + t * E + cg * C, vold);
+          st_vec<C>(svins + t * E + cg * C, ins);
+        }
+      }
+    }
+
+    if (has_next) {
+#pragma unroll
+      for (int u = 0; u < (T + P - 1) / P; ++u) {
+        const int i = tid + u * P;
+        if (i < nt_next) beta_buf((c + 1) & 1)[i] = bnext[u];
+      }
+    }
+    __syncthreads();
+    flush_rows<SM::ROW_IO, P>(p.out.row(n, h, t0), p.out.sl, so, nt, tid);
+    if (save) {
+      flush_rows<SM::ROW_F, P>(p.v_old.row(n, h, t0), p.v_old.sl, svold, nt, tid);
+      flush_rows<SM::ROW_F, P>(p.v_ins.row(n, h, t0), p.v_ins.sl, svins, nt, tid);
+    }
+  }
+
+  // final state back in place
+#pragma unroll
+  for (int i2 = 0; i2 < R2; ++i2) {
+    float a[C], b[C];
+#pragma unroll
+    for (int j = 0; j < C; ++j) unpack2(W[i2][j], a[j], b[j]);
+    st_vec<C>(Wg + (rg * R + 2 * i2) * E + cg * C, a);
+    st_vec<C>(Wg + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// Backward.  With G = dL/dW_t carried backwards in time and g = dL/dout_t:
+//   G += q^T g ; gq = W_t g ; r = k.G ; gv = beta r ; gbeta = r.(v - v_old)
+//   gk = G ins + W_{t-1} (-beta r) ; W_{t-1} = W_t - k^T ins ; G += k^T (-beta r)
+// (same arithmetic as fast_weight_cuda.cu:489-552 and :336-389, in one pass).
+// Column results (gv) are complete after the row-group shuffle; row results (gq, gk) and
+// gbeta are reduced across the column groups of a warp with shuffles, parked per warp in
+// shared memory and summed across warps when the chunk is written out -- they are outputs
+// only, so nothing on the recurrence's critical path waits for a barrier.
+// ---------------------------------------------------------------------------------------
+template <typename TIO, int E, int P, int T>
+struct DeltaBwdSmem {
+  static constexpr int NWARP = P / 32;
+  static constexpr int ROW_IO = E * (int)sizeof(TIO);
+  static constexpr int ROW_F = E * 4;
+  static constexpr int BETA_BYTES = ((T * 4 + 15) / 16) * 16;
+  // q,k,v,gout (io) + v_old, v_ins (f32) + beta
+  static constexpr int IN_BYTES = 4 * T * ROW_IO + 2 * T * ROW_F + BETA_BYTES;
+  static constexpr int GV_BYTES = T * ROW_IO;
+  static constexpr int PART_BYTES = T * NWARP * 2 * ROW_F;       // per-warp partial gq, gk
+  static constexpr int GB_BYTES = ((T * NWARP * 4 + 15) / 16) * 16;
+  static constexpr int TOTAL = 2 * IN_BYTES + GV_BYTES + PART_BYTES + GB_BYTES;
+};
+
+template <typename TIO, int E, int P, int R, int T, bool PK, int MINB>
+__global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams p) {
+  using TL = Tiling<E, P, R>;
+  using SM = DeltaBwdSmem<TIO, E, P, T>;
+  constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2, NWARP = TL::NWARP;
+  const int tid = threadIdx.x;
+  const int rg = tid % NRG, cg = tid / NRG;
+  const int warp = tid / 32, lane = tid % 32;
+  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
+
+  extern __shared__ __align__(16) unsigned char smem[];
+  unsigned char* s_o = smem + 2 * SM::IN_BYTES;
+  TIO* sgv = reinterpret_cast<TIO*>(s_o);
+  float* spart = reinterpret_cast<float*>(s_o + SM::GV_BYTES);          // [T][NWARP][2][E]
+  float* sgb = reinterpret_cast<float*>(s_o + SM::GV_BYTES + SM::PART_BYTES);  // [T][NWARP]
+
+  u64 W[R2][C], G[R2][C];
+  float* Wg = p.W.mat(n, h);
+#pragma unroll
+  for (int i2 = 0; i2 < R2; ++i2) {
+    float a[C], b[C];
+    ld_vec<C>(Wg + (rg * R + 2 * i2) * E + cg * C, a);
+    ld_vec<C>(Wg + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+#pragma unroll
+    for (int j = 0; j < C; ++j) { W[i2][j] = pack2(a[j], b[j]); G[i2][j] = 0ull; }
+  }
+
+  const int L = p.L;
+  const int nchunks = (L + T - 1) / T;
+  auto in_buf = [&](int b) { return smem + b * SM::IN_BYTES; };
+  auto stage_chunk = [&](int c) {
+    const int t0 = c * T, nt = min(T, L - t0);
+    unsigned char* ib = in_buf(c & 1);
+    stage_rows<SM::ROW_IO, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, tid);
+    stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.K.row(n, h, t0), p.K.sl, nt, tid);
+    stage_rows<SM::ROW_IO, P>(ib + 2 * T * SM::ROW_IO, p.V.row(n, h, t0), p.V.sl, nt, tid);
+    stage_rows<SM::ROW_IO, P>(ib + 3 * T * SM::ROW_IO, p.gout.row(n, h, t0), p.gout.sl, nt, tid);
+    unsigned char* fb = ib + 4 * T * SM::ROW_IO;
+    stage_rows<SM::ROW_F, P>(fb, p.v_old.row(n, h, t0), p.v_old.sl, nt, tid);
+    stage_rows<SM::ROW_F, P>(fb + T * SM::ROW_F, p.v_ins.row(n, h, t0), p.v_ins.sl, nt, tid);
+  };
+  auto beta_ld = [&](int c, int i) -> float {
+    return to_f32(*reinterpret_cast<const TIO*>(p.beta.row(n, h, c * T + i)));
+  };
+  auto beta_buf = [&](int b) {
+    return reinterpret_cast<float*>(in_buf(b) + 4 * T * SM::ROW_IO + 2 * T * SM::ROW_F);
+  };
+
+  {
+    const int c0 = nchunks - 1;
+    stage_chunk(c0);
+    cp_async_commit();
+    const int nt0 = L - c0 * T;
+    for (int i = tid; i < nt0; i += P) beta_buf(c0 & 1)[i] = beta_ld(c0, i);
+  }
+
+  for (int c = nchunks - 1; c >= 0; --c) {
+    const int t0 = c * T, nt = min(T, L - t0);
+    const bool has_next = (c > 0);
+    float bnext[(T + P - 1) / P];
+    if (has_next) {
+      stage_chunk(c - 1);   // full chunk of T steps
+#pragma unroll
+      for (int u = 0; u < (T + P - 1) / P; ++u) {
+        const int i = tid + u * P;
+        bnext[u] = (i < T) ? beta_ld(c - 1, i) : 0.f;
+      }
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+
+    const unsigned char* ib = in_buf(c & 1);
+    const TIO* sq = reinterpret_cast<const TIO*>(ib);
+    const TIO* sk = reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO);
+    const TIO* sv = reinterpret_cast<const TIO*>(ib + 2 * T * SM::ROW_IO);
+    const TIO* sg = reinterpret_cast<const TIO*>(ib + 3 * T * SM::ROW_IO);
+    const float* svo = reinterpret_cast<const float*>(ib + 4 * T * SM::ROW_IO);
+    const float* svi = svo + T * E;
+    const float* sb = beta_buf(c & 1);
+
+    for (int t = nt - 1; t >= 0; --t) {
+      float kr[R], qr[R], gc[C], insc[C], vc[C], voc[C];
+      ld_vec<R>(sk + t * E + rg * R, kr);
+      ld_vec<R>(sq + t * E + rg * R, qr);
+      ld_vec<C>(sg + t * E + cg * C, gc);
+      ld_vec<C>(svi + t * E + cg * C, insc);
+      ld_vec<C>(sv + t * E + cg * C, vc);
+      ld_vec<C>(svo + t * E + cg * C, voc);
+      const float bt = sb[t];
+
+      u64 k2[R2], gq2[R2], gk2[R2];
+#pragma unroll
+      for (int i2 = 0; i2 < R2; ++i2) {
+        k2[i2] = pack2(kr[2 * i2], kr[2 * i2 + 1]);
+        gq2[i2] = 0ull;
+        gk2[i2] = 0ull;
+      }
+      // G += q^T g ; gq partial = W_t g ; r partial = k.G
+      u64 ar[C];
+#pragma unroll
+      for (int j = 0; j < C; ++j) {
+        const u64 g2 = dup2(gc[j]);
+        ar[j] = 0ull;
+#pragma unroll
+        for (int i2 = 0; i2 < R2; ++i2) {
+          const u64 q2 = pack2(qr[2 * i2], qr[2 * i2 + 1]);
+          G[i2][j] = fma2<PK>(q2, g2, G[i2][j]);
+          gq2[i2] = fma2<PK>(W[i2][j], g2, gq2[i2]);
+          ar[j] = fma2<PK>(k2[i2], G[i2][j], ar[j]);
+        }
+      }
+      float gv[C], gb = 0.f;
+#pragma unroll
+      for (int j = 0; j < C; ++j) {
+        const float r = allreduce_rows<NRG>(hsum2(ar[j]));
+        gv[j] = bt * r;
+        gb = fmaf(r, vc[j] - voc[j], gb);
+      }
+      // gk partial = G ins + W_{t-1} (-gv) ; revert W ; G += k^T (-gv)
+#pragma unroll
+      for (int j = 0; j < C; ++j) {
+        const u64 ins2 = dup2(insc[j]);
+        const u64 ngv2 = dup2(-gv[j]);
+#pragma unroll
+        for (int i2 = 0; i2 < R2; ++i2) {
+          gk2[i2] = fma2<PK>(G[i2][j], ins2, gk2[i2]);
+          W[i2][j] = fma2<PK>(neg2(k2[i2]), ins2, W[i2][j]);
+          gk2[i2] = fma2<PK>(W[i2][j], ngv2, gk2[i2]);
+          G[i2][j] = fma2<PK>(k2[i2], ngv2, G[i2][j]);
+        }
+      }
+      if (rg == 0) st_vec<C>(sgv + t * E + cg * C, gv);
+      // row results: reduce across this warp's column groups, park per warp
+      float gqr[R], gkr[R];
+#pragma unroll
+      for (int i2 = 0; i2 < R2; ++i2) {
+        unpack2(gq2[i2], gqr[2 * i2], gqr[2 * i2 + 1]);
+        unpack2(gk2[i2], gkr[2 * i2], gkr[2 * i2 + 1]);
+      }
+#pragma unroll
+      for (int i = 0; i < R; ++i) {
+        gqr[i] = allreduce_cols<NRG>(gqr[i]);
+        gkr[i] = allreduce_cols<NRG>(gkr[i]);
+      }
+      gb = allreduce_cols<NRG>(rg == 0 ? gb : 0.f);
+      if (lane < NRG) {   // column group 0 of the warp: lane == rg
+        float* dst = spart + ((t * NWARP + warp) * 2) * E + rg * R;
+        st_vec<R>(dst, gqr);
+        st_vec<R>(dst + E, gkr);
+        if (lane == 0) sgb[t * NWARP + warp] = gb;
+      }
+    }
+
+    if (has_next) {
+#pragma unroll
+      for (int u = 0; u < (T + P - 1) / P; ++u) {
+        const int i = tid + u * P;
+        if (i < T) beta_buf((c - 1) & 1)[i] = bnext[u];
+      }
+    }
+    __syncthreads();
+    flush_rows<SM::ROW_IO, P>(p.gV.row(n, h, t0), p.gV.sl, sgv, nt, tid);
+    // combine the per-warp partial rows and write gq, gk (4 values per thread-iteration)
+    for (int idx = tid; idx < nt * 2 * (E / 4); idx += P) {
+      const int e4 = idx % (E / 4);
+      const int which = (idx / (E / 4)) % 2;
+      const int t = idx / (2 * (E / 4));
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int w = 0; w < NWARP; ++w) {
+        float v[4];
+        ld_vec<4>(spart + ((t * NWARP + w) * 2 + which) * E + e4 * 4, v);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] += v[u];
+      }
+      const SeqView& dstv = which ? p.gK : p.gQ;
+      st_vec<4>(reinterpret_cast<TIO*>(dstv.row(n, h, t0 + t)) + e4 * 4, acc);
+    }
+    for (int t = tid; t < nt; t += P) {
+      float s = 0.f;
+#pragma unroll
+      for (int w = 0; w < NWARP; ++w) s += sgb[t * NWARP + w];
+      from_f32(*reinterpret_cast<TIO*>(p.gbeta.row(n, h, t0 + t)), s);
+    }
+  }
+
+  // W now holds W_0: restore it in place (as the reference does); G is dL/dW_0.
+#pragma unroll
+  for (int i2 = 0; i2 < R2; ++i2) {
+    float a[C], b[C];
+#pragma unroll
+    for (int j = 0; j < C; ++j) unpack2(W[i2][j], a[j], b[j]);
+    st_vec<C>(Wg + (rg * R + 2 * i2) * E + cg * C, a);
+    st_vec<C>(Wg + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+  }
+  if (p.gW0.base != nullptr) {
+    float* Gg = p.gW0.mat(n, h);
+#pragma unroll
+    for (int i2 = 0; i2 < R2; ++i2) {
+      float a[C], b[C];
+#pragma unroll
+      for (int j = 0; j < C; ++j) unpack2(G[i2][j], a[j], b[j]);
+      st_vec<C>(Gg + (rg * R + 2 * i2) * E + cg * C, a);
+      st_vec<C>(Gg + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+    }
+  }
+}
+
+}  // namespace srwm

@@ -1,0 +1,131 @@
+"""ctypes binding of libsrwm_b200.so (declarations mirror include/srwm_b200.h).
+
+The library is prebuilt in-tree (``modern-srwm_b200/csrc/build.py``); there is no JIT
+compilation at import time and no fallback: if the shared object is missing, loading
+raises with the command that builds it.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libsrwm_b200.so")
+
+F32, BF16 = 0, 1
+FLAG_NO_SAVE, FLAG_STATE_GRAD_IN, FLAG_RESTORE_STATE = 1, 2, 4
+OP_SRWM_FWD, OP_SRWM_BWD, OP_DELTA_FWD, OP_DELTA_BWD = 0, 1, 2, 3
+
+ERR_NULL, ERR_SHAPE, ERR_HEAD_DIM, ERR_DTYPE, ERR_ALIGN, ERR_VARIANT, ERR_CUDA, ERR_TOO_LARGE = (
+    -1, -2, -3, -4, -5, -6, -7, -8)
+
+
+class Seq(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("stride_n", C.c_int64), ("stride_h", C.c_int64),
+                ("stride_l", C.c_int64)]
+
+
+class State(C.Structure):
+    _fields_ = [("data", C.c_void_p), ("stride_n", C.c_int64), ("stride_h", C.c_int64)]
+
+
+class SrwmFwdArgs(C.Structure):
+    _fields_ = [("N", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("E", C.c_int32),
+                ("io_dtype", C.c_int32), ("flags", C.c_uint32), ("variant", C.c_int32),
+                ("reserved", C.c_int32),
+                ("x", Seq), ("W_y", State), ("W_q", State), ("W_k", State), ("w_b", State),
+                ("out", Seq), ("q", Seq), ("k", Seq), ("beta", Seq),
+                ("y_diff", Seq), ("q_diff", Seq), ("k_diff", Seq), ("beta_diff", Seq)]
+
+
+class SrwmBwdArgs(C.Structure):
+    _fields_ = [("N", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("E", C.c_int32),
+                ("io_dtype", C.c_int32), ("flags", C.c_uint32), ("variant", C.c_int32),
+                ("reserved", C.c_int32),
+                ("x", Seq), ("q", Seq), ("k", Seq), ("beta", Seq),
+                ("y_diff", Seq), ("q_diff", Seq), ("k_diff", Seq), ("beta_diff", Seq),
+                ("grad_out", Seq),
+                ("W_y", State), ("W_q", State), ("W_k", State), ("w_b", State),
+                ("grad_x", Seq),
+                ("grad_W_y", State), ("grad_W_q", State), ("grad_W_k", State), ("grad_w_b", State)]
+
+
+class DeltaFwdArgs(C.Structure):
+    _fields_ = [("N", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("E", C.c_int32),
+                ("M", C.c_int32), ("io_dtype", C.c_int32), ("flags", C.c_uint32),
+                ("variant", C.c_int32),
+                ("Q", Seq), ("K", Seq), ("V", Seq), ("beta", Seq), ("W", State),
+                ("out", Seq), ("v_old", Seq), ("v_insert", Seq)]
+
+
+class DeltaBwdArgs(C.Structure):
+    _fields_ = [("N", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("E", C.c_int32),
+                ("M", C.c_int32), ("io_dtype", C.c_int32), ("flags", C.c_uint32),
+                ("variant", C.c_int32),
+                ("Q", Seq), ("K", Seq), ("V", Seq), ("beta", Seq),
+                ("v_old", Seq), ("v_insert", Seq), ("grad_out", Seq), ("W", State),
+                ("grad_Q", Seq), ("grad_K", Seq), ("grad_V", Seq), ("grad_beta", Seq),
+                ("grad_W0", State)]
+
+
+# name -> (restype, argtypes); also the list of symbols the header declares.
+SYMBOLS = {
+    "srwm_b200_srwm_forward": (C.c_int, [C.POINTER(SrwmFwdArgs), C.c_void_p]),
+    "srwm_b200_srwm_backward": (C.c_int, [C.POINTER(SrwmBwdArgs), C.c_void_p]),
+    "srwm_b200_delta_forward": (C.c_int, [C.POINTER(DeltaFwdArgs), C.c_void_p]),
+    "srwm_b200_delta_backward": (C.c_int, [C.POINTER(DeltaBwdArgs), C.c_void_p]),
+    "srwm_b200_reduce_batch": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_void_p,
+                                         C.c_int32, C.c_void_p]),
+    "srwm_b200_abi_version": (C.c_int, []),
+    "srwm_b200_head_dim_supported": (C.c_int, [C.c_int32]),
+    "srwm_b200_num_variants": (C.c_int, [C.c_int32, C.c_int32]),
+    "srwm_b200_strerror": (C.c_char_p, [C.c_int]),
+    "srwm_b200_last_cuda_error": (C.c_int, []),
+    "srwm_b200_describe": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32,
+                                     C.POINTER(C.c_int32 * 4)]),
+}
+
+_lib = None
+
+
+def load():
+    """Load the shared library once; raise loudly if it has not been built."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with "
+            "`python modern-srwm_b200/csrc/build.py` (there is no fallback implementation)")
+    lib = C.CDLL(LIB_PATH)
+    for name, (res, args) in SYMBOLS.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue        # optional symbols are checked by their users
+        fn.restype = res
+        fn.argtypes = args
+    if lib.srwm_b200_abi_version() != 1:
+        raise RuntimeError("libsrwm_b200.so ABI version mismatch")
+    _lib = lib
+    return lib
+
+
+class SrwmError(RuntimeError):
+    def __init__(self, code, what):
+        self.code = code
+        lib = load()
+        msg = lib.srwm_b200_strerror(code).decode()
+        if code == ERR_CUDA:
+            msg += f" [cudaError {lib.srwm_b200_last_cuda_error()}]"
+        super().__init__(f"{what}: {msg} (code {code})")
+
+
+def check(code, what):
+    if code != 0:
+        raise SrwmError(code, what)
+
+
+def describe(op, E, io_dtype=F32, variant=0):
+    out = (C.c_int32 * 4)()
+    check(load().srwm_b200_describe(op, E, io_dtype, variant, C.byref(out)), "describe")
+    return dict(P=out[0], R=out[1], T=out[2], smem=out[3])
