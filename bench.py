@@ -1,0 +1,509 @@
+#!/usr/bin/env python
+"""Benchmark of the SRWM / delta-rule hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+A "step" is one forward + backward pass of the operator over the (rank-local shard of the)
+workload's batch, followed by the reduction of the per-sample state gradients into the
+slow-weight gradient bucket and, for N > 1, its NCCL all-reduce.  The default workload is
+the scale-sweep configuration: SRWM, B=1024 (global, batch-sharded over the ranks), H=16,
+d_head=64, L=2048, bf16 activations, fp32 state.  The same run also times the delta-rule
+configuration of the sweep (B=512, H=16, d=64, L=8192) and reports it under "delta".
+
+Rank 0 prints ONE JSON line.  ``value`` is whole-job tokens/s (B*L / step time, max over
+ranks) with the inputs resident in HBM; ``e2e`` is the same metric through the public
+autograd entry point (``self_ref_v0``) with the activations starting in pinned host memory
+and the slow-weight gradients read back to the host every step.
+
+``--impl reference`` times the reference math (its per-step PyTorch loop with autograd,
+restated in oracle/srwm_oracle.py) on the host CPU cores, on a bounded sample of the same
+workload; rank 0 only.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "modern-srwm_b200"))
+
+import torch  # noqa: E402
+
+# ---- workloads (BASELINE.json configs; inputs are seeded synthetic tensors of those shapes) ----
+WORKLOADS = {
+    # name: op, B (global), H, L, E, dtype
+    "srwm_c5": dict(op="srwm", B=1024, H=16, L=2048, E=64, dtype="bf16"),
+    "delta_c5": dict(op="delta", B=512, H=16, L=8192, E=64, dtype="bf16"),
+    "srwm_c1": dict(op="srwm", B=4, H=4, L=64, E=16, dtype="f32"),
+    "delta_c2": dict(op="delta", B=32, H=8, L=512, E=64, dtype="f32"),
+    "srwm_c3op": dict(op="srwm", B=128, H=16, L=128, E=32, dtype="f32"),
+    # small cases for profiler captures (saved activations still exceed the 126 MB L2)
+    "srwm_prof": dict(op="srwm", B=32, H=16, L=512, E=64, dtype="bf16"),
+    "delta_prof": dict(op="delta", B=32, H=16, L=1024, E=64, dtype="bf16"),
+}
+
+# CPU sample sizes for the host baseline (same H, E, dtype=fp32 math; fewer sequences/steps)
+CPU_SAMPLE = {"srwm": dict(B=4, L=256), "delta": dict(B=4, L=512)}
+
+
+def algorithmic_bytes(op, E, s, per="fwd+bwd"):
+    """Bytes per (sequence, step) that the operator must move (s = bytes per activation
+    element), and bytes per sequence for the state; see DESIGN.md 'Roofline accounting'."""
+    D = 3 * E + 4
+    if op == "srwm":
+        fwd = E * s + E * s + (5 * E + 8) * 4              # x read, y write, saved write
+        bwd = 2 * E * s + E * s + (5 * E + 8) * 4          # x, dy read, dx write, saved read
+        st_f, st_b = 2 * E * D * 4, 2 * E * D * 4          # W0 read + W_L write ; W_L read + dW write
+    else:
+        fwd = (3 * E + 1) * s + E * s + 2 * E * 4          # q,k,v,beta read, out write, v_old/v_ins write
+        bwd = (3 * E + 1) * s + E * s + (3 * E + 1) * s + 2 * E * 4
+        st_f, st_b = 2 * E * E * 4, 2 * E * E * 4
+    if per == "fwd":
+        return fwd, st_f
+    if per == "bwd":
+        return bwd, st_b
+    return fwd + bwd, st_f + st_b
+
+
+def algorithmic_flops(op, E):
+    """Flops per (sequence, step), forward and backward (FMA = 2)."""
+    D = 3 * E + 4
+    n = E * D if op == "srwm" else E * E
+    return 6 * n, 14 * n
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as fh:
+            d = json.load(fh)
+        return float(d["hbm_gbs"]), "measured", float(d.get("sm_max_mhz", 1965.0))
+    return 6650.0, "fallback", 1965.0
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks / throttle reasons of one GPU while the timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.lines = []
+        self.proc = None
+        self.thr = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thr = threading.Thread(target=self._pump, daemon=True)
+        self.thr.start()
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons, power = [], [], set(), []
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[0])); mx.append(float(f[1])); power.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[4:8]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons),
+                "power_w_max": max(power), "samples": len(sm)}
+
+
+# ---------------------------------------------------------------------------------------
+# CPU reference arm / baseline
+# ---------------------------------------------------------------------------------------
+
+def cpu_reference_pass(op, H, E, B, L, seed=0):
+    """One forward+backward of the reference math (per-step PyTorch loop, autograd) in fp32
+    on the host cores.  Returns seconds."""
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import srwm_oracle as orc
+    g = torch.Generator().manual_seed(seed)
+    if op == "srwm":
+        x = torch.randn(B, H, L, E, generator=g).requires_grad_()
+        std = E ** -0.5
+        Ws = [(torch.randn(B, H, E, E, generator=g) * std).requires_grad_() for _ in range(3)]
+        Ws.append((torch.randn(B, H, E, 4, generator=g) * std).requires_grad_())
+        go = torch.randn(B, H, L, E, generator=g)
+        t0 = time.perf_counter()
+        out, _ = orc.srwm_loop(x, *Ws, update_last=False)
+        (out * go).sum().backward()
+        return time.perf_counter() - t0
+    Q = torch.softmax(torch.randn(B, H, L, E, generator=g), -1).requires_grad_()
+    K = torch.softmax(torch.randn(B, H, L, E, generator=g), -1).requires_grad_()
+    V = torch.randn(B, H, L, E, generator=g).requires_grad_()
+    Bt = torch.sigmoid(torch.randn(B, H, L, 1, generator=g)).requires_grad_()
+    W0 = torch.zeros(B, H, E, E)
+    go = torch.randn(B, H, L, E, generator=g)
+    t0 = time.perf_counter()
+    out, _ = orc.delta_loop(Q, K, V, Bt, W0)
+    (out * go).sum().backward()
+    return time.perf_counter() - t0
+
+
+def cpu_baseline(wl, runs=3):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    s = CPU_SAMPLE[wl["op"]]
+    cpu_reference_pass(wl["op"], wl["H"], wl["E"], s["B"], s["L"])   # warm-up (thread pool, allocator)
+    ts = [cpu_reference_pass(wl["op"], wl["H"], wl["E"], s["B"], s["L"]) for _ in range(runs)]
+    t = statistics.median(ts)
+    return {"value": s["B"] * s["L"] / t, "unit": "tokens/s", "cores": cores, "kind": "port",
+            "sample": f"{wl['op']} fwd+bwd, per-step PyTorch loop + autograd, fp32, B={s['B']} H={wl['H']} "
+                      f"L={s['L']} d={wl['E']} ({t:.1f} s per pass)"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    wl = WORKLOADS[args.workload]
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    s = CPU_SAMPLE[wl["op"]]
+    for _ in range(min(args.warmup, 1)):
+        cpu_reference_pass(wl["op"], wl["H"], wl["E"], s["B"], s["L"])
+    ts = [cpu_reference_pass(wl["op"], wl["H"], wl["E"], s["B"], s["L"], seed=i) for i in range(args.steps)]
+    t = sum(ts) / len(ts)
+    val = s["B"] * s["L"] / t
+    sample = (f"{wl['op']} fwd+bwd, reference per-step PyTorch loop + autograd on the host CPU, fp32, "
+              f"B={s['B']} H={wl['H']} L={s['L']} d={wl['E']}")
+    line = {"impl": "reference", "metric": "SRWM/delta fwd+bwd tokens/s", "value": val, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic", "config": config_of(args.workload, wl, args.gpus),
+            "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def config_of(name, wl, n):
+    return {"workload": f"{name}: {wl['op']} fwd+bwd B={wl['B']} H={wl['H']} L={wl['L']} d_head={wl['E']} "
+                        f"{wl['dtype']} activations, fp32 state",
+            "global_batch": wl["B"], "seq_len": wl["L"], "heads": wl["H"], "d_head": wl["E"],
+            "parallelism": f"batch-sharded x{n}", "l2": "inputs_exceed_l2"}
+
+
+# ---------------------------------------------------------------------------------------
+# our arm
+# ---------------------------------------------------------------------------------------
+
+class OpBench:
+    """Holds device-resident inputs of one workload shard and runs steps through the C ABI."""
+
+    def __init__(self, wl, Bl, device, seed):
+        import srwm_b200 as sb
+        from srwm_b200.dist import GradBucket
+        self.sb, self.wl, self.Bl, self.dev = sb, wl, Bl, device
+        H, L, E = wl["H"], wl["L"], wl["E"]
+        dt = torch.bfloat16 if wl["dtype"] == "bf16" else torch.float32
+        self.dt = dt
+        g = torch.Generator(device=device).manual_seed(seed)
+        rn = lambda *s: torch.randn(*s, device=device, dtype=torch.float32, generator=g)
+        self.launches_per_step = 0
+        if wl["op"] == "srwm":
+            self.x = self._big_randn((Bl, H, L, E), g, dt)
+            self.go = self._big_randn((Bl, H, L, E), g, dt)
+            std = E ** -0.5
+            self.slow = [rn(1, H, E, E) * std for _ in range(3)] + [rn(1, H, E, 4) * std]
+            self.state = [torch.empty(Bl, H, E, w.shape[-1], device=device) for w in self.slow]
+            self.bucket = GradBucket([w.shape[1:] for w in self.slow], device)
+        else:
+            self.Q = self._big_randn((Bl, H, L, E), g, dt, softmax=True)
+            self.K = self._big_randn((Bl, H, L, E), g, dt, softmax=True)
+            self.V = self._big_randn((Bl, H, L, E), g, dt)
+            self.Bt = torch.sigmoid(rn(Bl, H, L, 1)).to(dt)
+            self.go = self._big_randn((Bl, H, L, E), g, dt)
+            self.W = torch.zeros(Bl, H, E, E, device=device)
+            self.bucket = None
+        self.ev = []
+
+    @staticmethod
+    def _big_randn(shape, g, dt, softmax=False):
+        """Generate N(0,1) (optionally softmax over the feature dim) in batch slices to bound
+        the fp32 temporary."""
+        out = torch.empty(shape, device=g.device, dtype=dt)
+        step = max(1, (1 << 28) // max(1, out[0].numel()))
+        for i in range(0, shape[0], step):
+            t = torch.randn((min(step, shape[0] - i),) + tuple(shape[1:]), device=g.device, generator=g)
+            if softmax:
+                t = torch.softmax(t, -1)
+            out[i:i + step] = t.to(dt)
+        return out
+
+    def step(self, timed=False):
+        sb = self.sb
+        rec = None
+        if timed:
+            rec = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        if self.wl["op"] == "srwm":
+            for s, w in zip(self.state, self.slow):
+                s.copy_(w.expand_as(s))
+            if rec: rec[0].record()
+            out, saved = sb.srwm_forward(self.x, *self.state)
+            if rec: rec[1].record()
+            grads = sb.srwm_backward(self.x, saved, self.go, *self.state)
+            if rec: rec[2].record()
+            for i in range(4):
+                self.bucket.reduce_into(i, grads[1 + i])
+            self.bucket.all_reduce()
+            self.last = (out, grads[0])
+            self.launches_per_step = 2 + 4
+        else:
+            self.W.zero_()
+            if rec: rec[0].record()
+            out, saved = sb.delta_forward(self.Q, self.K, self.V, self.Bt, self.W)
+            if rec: rec[1].record()
+            grads = sb.delta_backward(self.Q, self.K, self.V, self.Bt, saved, self.go, self.W)
+            if rec: rec[2].record()
+            self.last = (out, grads[0])
+            self.launches_per_step = 2
+        if rec:
+            self.ev.append(rec)
+
+    def kernel_ms(self):
+        f = [a.elapsed_time(b) for a, b, _ in self.ev]
+        b = [b_.elapsed_time(c) for _, b_, c in self.ev]
+        return sum(f) / len(f), sum(b) / len(b)
+
+
+def timed_region(fn, steps, warmup, dist_on, device):
+    import torch.distributed as dist
+    for _ in range(warmup):
+        fn(False)
+    torch.cuda.synchronize(device)
+    if dist_on:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        fn(True)
+    e1.record()
+    torch.cuda.synchronize(device)
+    if dist_on:
+        dist.barrier()
+    torch.cuda.synchronize(device)
+    ms = e0.elapsed_time(e1)
+    if dist_on:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    return ms / steps
+
+
+def run_e2e(wl, Bl, device, steps, warmup, dist_on):
+    """Same metric through the public autograd entry point with host-resident activations:
+    per step, H2D copy of the activations from pinned memory, forward, backward, batch
+    reduction of the slow-weight gradients (autograd's repeat-backward), all-reduce, and a
+    D2H read of those gradients."""
+    import torch.distributed as dist
+    import srwm_b200 as sb
+    H, L, E = wl["H"], wl["L"], wl["E"]
+    dt = torch.bfloat16 if wl["dtype"] == "bf16" else torch.float32
+    g = torch.Generator().manual_seed(7)
+    if wl["op"] == "srwm":
+        hx = torch.empty((Bl, H, L, E), dtype=dt).pin_memory()
+        chunk = max(1, (1 << 26) // (H * L * E))
+        for i in range(0, Bl, chunk):
+            hx[i:i + chunk] = torch.randn((min(chunk, Bl - i), H, L, E), generator=g).to(dt)
+        go = torch.randn((Bl, H, L, E), device=device, dtype=dt)
+        std = E ** -0.5
+        slow = [(torch.randn(1, H, E, E, device=device) * std).requires_grad_() for _ in range(3)]
+        slow.append((torch.randn(1, H, E, 4, device=device) * std).requires_grad_())
+        nflat = sum(w.numel() for w in slow)
+        hgrad = torch.empty(nflat, dtype=torch.float32).pin_memory()
+        dx = torch.empty((Bl, H, L, E), device=device, dtype=dt)
+        h2d = hx.numel() * hx.element_size()
+        d2h = nflat * 4
+
+        def step(_timed):
+            dx.copy_(hx, non_blocking=True)
+            x = dx.detach().requires_grad_()
+            Wb = [w.repeat(Bl, 1, 1, 1) for w in slow]
+            out = sb.self_ref_v0(x, *Wb)
+            out.backward(go)
+            flat = torch.cat([w.grad.reshape(-1) for w in slow])
+            if dist_on:
+                dist.all_reduce(flat)
+            hgrad.copy_(flat, non_blocking=True)
+            for w in slow:
+                w.grad = None
+            torch.cuda.current_stream().synchronize()
+    else:
+        hq, hk, hv = (torch.empty((Bl, H, L, E), dtype=dt).pin_memory() for _ in range(3))
+        hb = torch.empty((Bl, H, L, 1), dtype=dt).pin_memory()
+        chunk = max(1, (1 << 26) // (H * L * E))
+        for i in range(0, Bl, chunk):
+            n = min(chunk, Bl - i)
+            hq[i:i + n] = torch.softmax(torch.randn((n, H, L, E), generator=g), -1).to(dt)
+            hk[i:i + n] = torch.softmax(torch.randn((n, H, L, E), generator=g), -1).to(dt)
+            hv[i:i + n] = torch.randn((n, H, L, E), generator=g).to(dt)
+            hb[i:i + n] = torch.sigmoid(torch.randn((n, H, L, 1), generator=g)).to(dt)
+        go = torch.randn((Bl, H, L, E), device=device, dtype=dt)
+        dq, dk, dv = (torch.empty((Bl, H, L, E), device=device, dtype=dt) for _ in range(3))
+        db = torch.empty((Bl, H, L, 1), device=device, dtype=dt)
+        W = torch.zeros(Bl, H, E, E, device=device)
+        hres = torch.empty(Bl * H, dtype=torch.float32).pin_memory()
+        h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hb))
+        d2h = hres.numel() * 4
+
+        def step(_timed):
+            dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True)
+            dv.copy_(hv, non_blocking=True); db.copy_(hb, non_blocking=True)
+            q, k, v, b = (t.detach().requires_grad_() for t in (dq, dk, dv, db))
+            W.zero_()
+            out = sb.fast_weight_delta(q, k, v, b, W)
+            out.backward(go)
+            # per-sequence summary of the gradient as the step's result
+            hres.copy_(b.grad.float().sum(dim=(2, 3)).reshape(-1), non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+
+    ms = timed_region(step, steps, warmup, dist_on, device)
+    return ms, h2d, d2h
+
+
+def run_ours(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU fallback for the operators)")
+    device = torch.device("cuda", local_rank)
+    torch.cuda.set_device(device)
+    dist_on = world > 1
+    if dist_on:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    from srwm_b200.dist import shard_range
+    n = world
+    results = {}
+    clocks = None
+    names = [args.workload] + ([] if args.no_delta or args.workload != "srwm_c5" else ["delta_c5"])
+    hbm_peak, peak_kind, _ = load_peaks()
+    for name in names:
+        wl = WORKLOADS[name]
+        lo, hi = shard_range(wl["B"], n, rank)
+        Bl = hi - lo
+        ob = OpBench(wl, Bl, device, seed=1000 + rank)
+        sampler = ClockSampler(local_rank) if (rank == 0 and name == names[0]) else None
+        if sampler:
+            sampler.start()
+        ms = timed_region(ob.step, args.steps, args.warmup, dist_on, device)
+        if sampler:
+            clocks = sampler.stop()
+        fwd_ms, bwd_ms = ob.kernel_ms()
+        launches = ob.launches_per_step * args.steps
+        del ob
+        torch.cuda.empty_cache()
+        e2e_ms, h2d, d2h = (None, 0, 0)
+        if not args.no_e2e:
+            e2e_ms, h2d, d2h = run_e2e(wl, Bl, device, max(1, min(args.steps, args.e2e_steps)), min(args.warmup, 3),
+                                       dist_on)
+            torch.cuda.empty_cache()
+        tokens = wl["B"] * wl["L"]
+        s = 2 if wl["dtype"] == "bf16" else 4
+        seqs_local = Bl * wl["H"]
+        per_step, per_seq = algorithmic_bytes(wl["op"], wl["E"], s, "bwd")
+        bwd_bytes = seqs_local * (wl["L"] * per_step + per_seq)
+        ff, fb = algorithmic_flops(wl["op"], wl["E"])
+        achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        results[name] = dict(
+            wl=wl, ms=ms, tokens_per_s=tokens / (ms * 1e-3), fwd_ms=fwd_ms, bwd_ms=bwd_ms, launches=launches,
+            e2e=None if e2e_ms is None else {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
+                                             "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                                             "ms_per_step": e2e_ms},
+            roofline={"bound": "hbm", "kernel": f"{wl['op']}_bwd_kernel", "achieved": achieved, "peak": hbm_peak,
+                      "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": f"of {peak_kind}",
+                      "traffic": NCU_TRAFFIC.get(name),
+                      "algorithmic_bytes_per_launch": bwd_bytes, "launch_ms": bwd_ms},
+            fp32={"fwd_tflops": seqs_local * wl["L"] * ff / (fwd_ms * 1e-3) / 1e12,
+                  "bwd_tflops": seqs_local * wl["L"] * fb / (bwd_ms * 1e-3) / 1e12,
+                  "note": "algorithmic flops / kernel time; CUDA-core fp32 peak is 148 SMs x 128 lanes x 2 x clock"})
+    if rank == 0:
+        main = results[names[0]]
+        wl = main["wl"]
+        line = {"metric": "SRWM/delta fwd+bwd tokens/s", "value": main["tokens_per_s"], "unit": "tokens/s",
+                "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms"],
+                "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "f32 state / " + wl["dtype"] + " activations", "data": "synthetic",
+                "config": config_of(names[0], wl, n), "roofline": main["roofline"], "fp32": main["fp32"],
+                "kernel_ms": {"fwd": main["fwd_ms"], "bwd": main["bwd_ms"]},
+                "gpu_launches": main["launches"], "clocks": clocks}
+        if main["e2e"] is not None:
+            line["e2e"] = main["e2e"]
+        if n == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(wl)
+        for extra in names[1:]:
+            r = results[extra]
+            line["delta"] = {"value": r["tokens_per_s"], "unit": "tokens/s", "ms_per_step": r["ms"],
+                             "config": config_of(extra, r["wl"], n), "roofline": r["roofline"], "fp32": r["fp32"],
+                             "kernel_ms": {"fwd": r["fwd_ms"], "bwd": r["bwd_ms"]}, "gpu_launches": r["launches"],
+                             "e2e": r["e2e"]}
+            if n == 1 and not args.no_cpu:
+                line["delta"]["cpu_baseline"] = cpu_baseline(r["wl"])
+        print(json.dumps(line), flush=True)
+    if dist_on:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+# DRAM bytes per launch of the backward kernel from ncu captures (dram__bytes_read.sum +
+# dram__bytes_write.sum), scaled to the full workload by sequence-steps; see profiles/.
+NCU_TRAFFIC = {}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--workload", default="srwm_c5", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-delta", action="store_true", help="skip the delta-rule sweep configuration")
+    ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
