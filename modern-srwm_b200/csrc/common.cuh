@@ -199,6 +199,26 @@ __device__ __forceinline__ float allreduce_warp(float v) {
   return v;
 }
 
+// Reduce-scatter of v[0..N) across the K lanes {lane ^ (m*STRIDE)}, m < K (K a power of two
+// dividing N).  On return the lane whose index along that axis is a = (lane/STRIDE) % K
+// holds in v[0..N/K) the sums of elements [a*N/K, (a+1)*N/K).  N*(1-1/K) shuffles instead of
+// the N*log2(K) of a butterfly all-reduce.
+template <int N, int K, int STRIDE, int NV>
+__device__ __forceinline__ void reduce_scatter(float (&v)[NV], int lane) {
+  static_assert(N % K == 0 && N <= NV, "bad reduce_scatter shape");
+  if constexpr (K > 1) {
+    constexpr int n = N / 2, k = K / 2;
+    const bool up = ((lane / STRIDE) & k) != 0;
+#pragma unroll
+    for (int i = 0; i < n; ++i) {
+      const float send = up ? v[i] : v[i + n];
+      const float keep = up ? v[i + n] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, k * STRIDE);
+    }
+    reduce_scatter<n, k, STRIDE, NV>(v, lane);
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // Asynchronous global -> shared staging of `nrows` rows of ROWBYTES bytes each (16-byte
 // pieces, cp.async.cg: bypasses L1), and the matching shared -> global flush.

@@ -11,30 +11,35 @@
   X(8, 0, 32, 2, 16, true, 8)    \
   X(16, 0, 32, 4, 16, true, 8)   \
   X(16, 1, 32, 2, 16, true, 8)   \
-  X(32, 0, 64, 8, 16, true, 6)   \
-  X(32, 1, 32, 8, 16, true, 8)   \
-  X(32, 2, 64, 4, 16, true, 6)   \
-  X(32, 3, 128, 8, 16, true, 4)  \
-  X(64, 0, 128, 8, 16, true, 3)  \
-  X(64, 1, 128, 16, 16, true, 3) \
-  X(64, 2, 256, 8, 16, true, 2)  \
-  X(64, 3, 128, 8, 16, false, 3) \
-  X(64, 4, 256, 16, 16, true, 2)
+  X(32, 1, 64, 8, 16, true, 6)   \
+  X(32, 2, 32, 8, 16, true, 8)   \
+  X(32, 3, 64, 4, 16, true, 6)   \
+  X(64, 1, 128, 8, 16, true, 3)  \
+  X(64, 2, 128, 16, 16, true, 3) \
+  X(64, 3, 128, 8, 16, false, 3)
+
+// Column-layout forward (96 threads): Y(E, variant, T, PK, MINB, DPRE)
+//   DPRE  the k warp publishes q-k once per step (two-warp named barrier) instead of every
+//         thread recomputing it in the second pass
+#define SRWM_FWD_COL_CONFIGS(Y)  \
+  Y(64, 0, 16, true, 4, false)   \
+  Y(64, 4, 16, true, 3, false)   \
+  Y(64, 5, 16, false, 4, false)  \
+  Y(64, 6, 16, true, 4, true)    \
+  Y(32, 0, 16, true, 8, false)   \
+  Y(32, 4, 16, true, 12, false)  \
+  Y(32, 5, 16, true, 8, true)
 
 #define SRWM_BWD_CONFIGS(X)      \
   X(8, 0, 32, 2, 16, true, 8)    \
-  X(16, 0, 32, 4, 16, true, 8)   \
-  X(16, 1, 32, 2, 16, true, 8)   \
-  X(32, 0, 64, 8, 16, true, 6)   \
-  X(32, 1, 64, 4, 16, true, 6)   \
+  X(16, 0, 32, 2, 16, true, 8)   \
+  X(16, 1, 32, 4, 16, true, 8)   \
+  X(32, 0, 64, 4, 16, true, 6)   \
+  X(32, 1, 64, 8, 16, true, 6)   \
   X(32, 2, 32, 8, 16, true, 8)   \
-  X(32, 3, 128, 8, 16, true, 4)  \
   X(64, 0, 128, 8, 16, true, 2)  \
   X(64, 1, 256, 8, 16, true, 1)  \
-  X(64, 2, 256, 4, 16, true, 1)  \
-  X(64, 3, 128, 8, 16, false, 2) \
-  X(64, 4, 128, 16, 16, true, 2) \
-  X(64, 5, 512, 8, 8, true, 1)
+  X(64, 2, 128, 8, 16, false, 2)
 
 #define DELTA_FWD_CONFIGS(X)     \
   X(8, 0, 32, 2, 16, true, 8)    \
@@ -53,8 +58,8 @@
   X(16, 0, 32, 4, 16, true, 8)   \
   X(32, 0, 32, 8, 16, true, 10)  \
   X(32, 1, 64, 8, 16, true, 8)   \
-  X(64, 0, 64, 16, 8, true, 4)   \
+  X(64, 0, 64, 8, 8, true, 4)    \
   X(64, 1, 128, 8, 8, true, 4)   \
   X(64, 2, 128, 16, 8, true, 4)  \
-  X(64, 3, 64, 8, 8, true, 4)    \
-  X(64, 4, 64, 16, 8, false, 4)
+  X(64, 3, 64, 16, 8, true, 4)   \
+  X(64, 4, 64, 8, 8, false, 4)

@@ -278,6 +278,249 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
 }
 
 // ---------------------------------------------------------------------------------------
+// Forward, column layout (E = 32 or 64; 96 threads).  Warp 0 owns W_y, warp 1 W_q, warp 2
+// W_k; lane l holds E/32 whole columns (all E rows) of its block as row pairs.  Both
+// matvec passes and the rank-1 update are then thread-local -- no shuffle reductions --
+// with the operand vector (x, q-k, k) read from shared memory as 16-byte broadcasts.  The
+// q~ / k~ values of a step land 2 per lane in the warp that owns the block, exactly the
+// shape of a warp-level softmax (one redux.sync max, one shuffle-tree sum), and warp 0
+// meanwhile handles the four w_b columns (lane = column j x an eighth of the rows).
+// One block-wide barrier per step (q, k, beta published through the output staging rows).
+// ---------------------------------------------------------------------------------------
+template <typename TIO, int E, int T>
+struct SrwmFwdColSmem {
+  static constexpr int ROW_IO = E * (int)sizeof(TIO);
+  static constexpr int ROW_F = E * 4;
+  static constexpr int IN_BYTES = T * ROW_IO;
+  static constexpr int XF_BYTES = sizeof(TIO) == 4 ? 0 : T * ROW_F;   // x converted to fp32
+  static constexpr int OUT_BYTES = T * ROW_IO + 5 * T * ROW_F + 2 * T * 16;
+  static constexpr int WB_BYTES = 4 * ROW_F;
+  static constexpr int DQ_BYTES = 2 * ROW_F;                          // q - k, double buffered
+  static constexpr int TOTAL = 2 * IN_BYTES + XF_BYTES + OUT_BYTES + WB_BYTES + DQ_BYTES;
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+template <typename TIO, int E, int T, bool PK, int MINB, bool DPRE>
+__global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdParams p) {
+  static_assert(E == 32 || E == 64, "column layout needs a whole warp of columns per block");
+  using SM = SrwmFwdColSmem<TIO, E, T>;
+  constexpr int P = 96, CPL = E / 32, E2 = E / 2, RB = E / 8;
+  const int tid = threadIdx.x;
+  const int warp = tid / 32, lane = tid % 32;
+  const int c0 = lane * CPL;
+  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
+  const bool save = !(p.flags & 1u);
+  const int jb = lane / 8, r8 = lane % 8;   // warp 0: w_b column / row eighth of this lane
+
+  extern __shared__ __align__(16) unsigned char smem[];
+  float* xf32 = reinterpret_cast<float*>(smem + 2 * SM::IN_BYTES);
+  unsigned char* s_o = smem + 2 * SM::IN_BYTES + SM::XF_BYTES;
+  TIO* sy = reinterpret_cast<TIO*>(s_o);
+  float* sq = reinterpret_cast<float*>(s_o + T * SM::ROW_IO);
+  float* sk = sq + T * E;
+  float* syd = sk + T * E;
+  float* sqd = syd + T * E;
+  float* skd = sqd + T * E;
+  float* sbeta = skd + T * E;   // [T][4]
+  float* sbd = sbeta + T * 4;   // [T][4]
+  float* wbT = sbd + T * 4;     // [4][E]
+  float* sdq = wbT + 4 * E;     // [2][E]  q - k of the current step (DPRE)
+  float* sdz = warp == 0 ? syd : (warp == 1 ? sqd : skd);
+
+  u64 W[E2][CPL];
+  float* gW = (warp == 0 ? p.Wy : (warp == 1 ? p.Wq : p.Wk)).mat(n, h);
+  float* gwb = p.wb.mat(n, h);
+#pragma unroll
+  for (int e2 = 0; e2 < E2; ++e2) {
+    float a[CPL], b[CPL];
+    ld_vec<CPL>(gW + (2 * e2) * E + c0, a);
+    ld_vec<CPL>(gW + (2 * e2 + 1) * E + c0, b);
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) W[e2][c] = pack2(a[c], b[c]);
+  }
+  for (int i = tid; i < 4 * E; i += P) wbT[(i % 4) * E + i / 4] = gwb[i];
+
+  const int L = p.L;
+  const int nchunks = (L + T - 1) / T;
+  auto in_buf = [&](int b) { return reinterpret_cast<TIO*>(smem + b * SM::IN_BYTES); };
+  auto stage_chunk = [&](int c) {
+    const int t0 = c * T, nt = min(T, L - t0);
+    stage_rows<SM::ROW_IO, P>(in_buf(c & 1), p.x.row(n, h, t0), p.x.sl, nt, tid);
+  };
+  stage_chunk(0);
+  cp_async_commit();
+  const u64 neg1 = pack2(-1.f, -1.f);
+  int par = 0;
+
+  for (int c = 0; c < nchunks; ++c) {
+    const int t0 = c * T, nt = min(T, L - t0);
+    if (c + 1 < nchunks) stage_chunk(c + 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const float* sxf;
+    if constexpr (sizeof(TIO) == 4) {
+      sxf = reinterpret_cast<const float*>(in_buf(c & 1));
+    } else {
+      const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(in_buf(c & 1));
+      for (int i = tid; i < nt * E / 2; i += P) {
+        float v[2];
+        ld_vec<2>(xb + 2 * i, v);
+        st_vec<2>(xf32 + 2 * i, v);
+      }
+      __syncthreads();
+      sxf = xf32;
+    }
+
+    for (int t = 0; t < nt; ++t, par ^= 1) {
+      const float* xr = sxf + t * E;
+      const float* qr = sq + t * E;
+      const float* kr = sk + t * E;
+      float* dq = sdq + par * E;
+      // ---- pass 1: this lane's columns of x.W ---------------------------------------------
+      u64 a0[CPL], a1[CPL];
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) { a0[cc] = 0ull; a1[cc] = 0ull; }
+#pragma unroll
+      for (int e4 = 0; e4 < E / 4; ++e4) {
+        const float4 xv = reinterpret_cast<const float4*>(xr)[e4];
+        const u64 p0 = pack2(xv.x, xv.y), p1 = pack2(xv.z, xv.w);
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) {
+          a0[cc] = fma2<PK>(p0, W[2 * e4][cc], a0[cc]);
+          a1[cc] = fma2<PK>(p1, W[2 * e4 + 1][cc], a1[cc]);
+        }
+      }
+      float v[CPL];
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) v[cc] = hsum2(a0[cc]) + hsum2(a1[cc]);
+      if (warp == 0) {
+        st_vec<CPL>(sy + t * E + c0, v);
+        float xrow[RB], wrow[RB];
+        ld_vec<RB>(xr + r8 * RB, xrow);
+        ld_vec<RB>(wbT + jb * E + r8 * RB, wrow);
+        float pb = 0.f;
+#pragma unroll
+        for (int i = 0; i < RB; ++i) pb = fmaf(xrow[i], wrow[i], pb);
+        pb = allreduce_rows<8>(pb);
+        if (r8 == 0) sbeta[t * 4 + jb] = fast_sigmoid(pb);
+      } else {
+        float m = v[0];
+#pragma unroll
+        for (int cc = 1; cc < CPL; ++cc) m = fmaxf(m, v[cc]);
+        m = warp_max(m);
+        float ssum = 0.f;
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) { v[cc] = __expf(v[cc] - m); ssum += v[cc]; }
+        ssum = allreduce_warp(ssum);
+        const float inv = __fdividef(1.f, ssum);
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) v[cc] *= inv;
+        st_vec<CPL>((warp == 1 ? sq : sk) + t * E + c0, v);
+        if constexpr (DPRE) {
+          // the k warp publishes q - k once for everybody: it needs q from the q warp,
+          // handed over through a two-warp named barrier
+          asm volatile("bar.sync 1, 64;" ::: "memory");
+          if (warp == 2) {
+            float qv[CPL];
+            ld_vec<CPL>(qr + c0, qv);
+#pragma unroll
+            for (int cc = 0; cc < CPL; ++cc) qv[cc] -= v[cc];
+            st_vec<CPL>(dq + c0, qv);
+          }
+        }
+      }
+      __syncthreads();
+
+      // ---- pass 2: d_Z = (q - k).W_Z --------------------------------------------------------
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) { a0[cc] = 0ull; a1[cc] = 0ull; }
+#pragma unroll
+      for (int e4 = 0; e4 < E / 4; ++e4) {
+        u64 d0, d1;
+        if constexpr (DPRE) {
+          const float4 dv = reinterpret_cast<const float4*>(dq)[e4];
+          d0 = pack2(dv.x, dv.y);
+          d1 = pack2(dv.z, dv.w);
+        } else {
+          const float4 qv = reinterpret_cast<const float4*>(qr)[e4];
+          const float4 kv = reinterpret_cast<const float4*>(kr)[e4];
+          d0 = fma2<PK>(pack2(kv.x, kv.y), neg1, pack2(qv.x, qv.y));
+          d1 = fma2<PK>(pack2(kv.z, kv.w), neg1, pack2(qv.z, qv.w));
+        }
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) {
+          a0[cc] = fma2<PK>(d0, W[2 * e4][cc], a0[cc]);
+          a1[cc] = fma2<PK>(d1, W[2 * e4 + 1][cc], a1[cc]);
+        }
+      }
+      const float bz = sbeta[t * 4 + warp];
+      u64 ins2[CPL];
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) {
+        v[cc] = hsum2(a0[cc]) + hsum2(a1[cc]);
+        ins2[cc] = dup2(bz * v[cc]);
+      }
+      st_vec<CPL>(sdz + t * E + c0, v);
+      if (warp == 0) {   // w_b column jb, rows of this lane
+        float qrow[RB], krow[RB], wrow[RB];
+        ld_vec<RB>(qr + r8 * RB, qrow);
+        ld_vec<RB>(kr + r8 * RB, krow);
+        ld_vec<RB>(wbT + jb * E + r8 * RB, wrow);
+        float db = 0.f;
+#pragma unroll
+        for (int i = 0; i < RB; ++i) db = fmaf(qrow[i] - krow[i], wrow[i], db);
+        db = allreduce_rows<8>(db);
+        if (r8 == 0) sbd[t * 4 + jb] = db;
+        const float ib = sbeta[t * 4 + 3] * db;
+#pragma unroll
+        for (int i = 0; i < RB; ++i) wrow[i] = fmaf(krow[i], ib, wrow[i]);
+        st_vec<RB>(wbT + jb * E + r8 * RB, wrow);
+      }
+      // ---- rank-1 update -------------------------------------------------------------------
+#pragma unroll
+      for (int e4 = 0; e4 < E / 4; ++e4) {
+        const float4 kv = reinterpret_cast<const float4*>(kr)[e4];
+        const u64 k0 = pack2(kv.x, kv.y), k1 = pack2(kv.z, kv.w);
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) {
+          W[2 * e4][cc] = fma2<PK>(k0, ins2[cc], W[2 * e4][cc]);
+          W[2 * e4 + 1][cc] = fma2<PK>(k1, ins2[cc], W[2 * e4 + 1][cc]);
+        }
+      }
+    }
+
+    __syncthreads();
+    flush_rows<SM::ROW_IO, P>(p.out.row(n, h, t0), p.out.sl, sy, nt, tid);
+    if (save) {
+      flush_rows<SM::ROW_F, P>(p.q.row(n, h, t0), p.q.sl, sq, nt, tid);
+      flush_rows<SM::ROW_F, P>(p.k.row(n, h, t0), p.k.sl, sk, nt, tid);
+      flush_rows<SM::ROW_F, P>(p.yd.row(n, h, t0), p.yd.sl, syd, nt, tid);
+      flush_rows<SM::ROW_F, P>(p.qd.row(n, h, t0), p.qd.sl, sqd, nt, tid);
+      flush_rows<SM::ROW_F, P>(p.kd.row(n, h, t0), p.kd.sl, skd, nt, tid);
+      flush_rows<16, P>(p.beta.row(n, h, t0), p.beta.sl, sbeta, nt, tid);
+      flush_rows<16, P>(p.bd.row(n, h, t0), p.bd.sl, sbd, nt, tid);
+    }
+  }
+
+#pragma unroll
+  for (int e2 = 0; e2 < E2; ++e2) {
+    float a[CPL], b[CPL];
+#pragma unroll
+    for (int cc = 0; cc < CPL; ++cc) unpack2(W[e2][cc], a[cc], b[cc]);
+    st_vec<CPL>(gW + (2 * e2) * E + c0, a);
+    st_vec<CPL>(gW + (2 * e2 + 1) * E + c0, b);
+  }
+  __syncthreads();
+  for (int i = tid; i < 4 * E; i += P) gwb[i] = wbT[(i % 4) * E + i / 4];
+}
+
+// ---------------------------------------------------------------------------------------
 // Backward (reverse time).  With G_Z = dL/dW_Z after the update of step t, g = dL/dy_t:
 //   ins_Z = b_Z d_Z ;  W_Z -= k^T ins_Z                       (rebuilds W(t-1))
 //   r_Z = k.G_Z ; gd_Z = b_Z r_Z ; gb~_Z = b_Z(1-b_Z) r_Z.d_Z
@@ -307,12 +550,19 @@ template <typename TIO, int E, int P, int R, int T, bool PK, int MINB>
 __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p) {
   using TL = Tiling<E, P, R>;
   using SM = SrwmBwdSmem<TIO, E, P, T>;
-  constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2, NWARP = TL::NWARP;
+  constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2, NWARP = TL::NWARP, CGW = TL::CGW;
+  // Row sums and scalars leave the warp through reduce-scatters when the tile shape allows
+  // it (every lane ends up with a distinct piece); otherwise through butterfly all-reduces.
+  constexpr bool SCATTER = (CGW >= 2) && (R % CGW == 0) && (8 % NRG == 0);
+  constexpr int S_ROW = SCATTER ? (2 * R) / CGW : R;   // [u | gk] values per lane after the scatter
+  constexpr int S_GX = SCATTER ? R / CGW : R;
+  constexpr int S_SC = SCATTER ? 8 / NRG : 8;
   const int tid = threadIdx.x;
   const int rg = tid % NRG, cg = tid / NRG;
   const int warp = tid / 32, lane = tid % 32;
+  const int cgl = lane / NRG;
   const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
-  const int jb = (cg % TL::BETA_CG_STEP == 0) ? cg / TL::BETA_CG_STEP : -1;
+  const int jb = cg < 4 ? cg : -1;   // column groups 0..3 (warp 0 when NRG <= 8) own w_b columns 0..3
 
   extern __shared__ __align__(16) unsigned char smem[];
   unsigned char* s_o = smem + 2 * SM::IN_BYTES;
@@ -391,139 +641,162 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
 
     for (int t = nt - 1; t >= 0; --t, par ^= 1) {
       // ================= phase 1 =================
-      float kr[R], qr[R];
-      ld_vec<R>(sk + t * E + rg * R, kr);
-      ld_vec<R>(sq + t * E + rg * R, qr);
-      float beta[4], bdv[4];
+      float beta[4];
       ld_vec<4>(sbeta + t * 4, beta);
-      ld_vec<4>(sbd + t * 4, bdv);
-      float dyc[C], dqc[C], dkc[C];
-      ld_vec<C>(syd + t * E + cg * C, dyc);
-      ld_vec<C>(sqd + t * E + cg * C, dqc);
-      ld_vec<C>(skd + t * E + cg * C, dkc);
-
-      u64 k2[R2], gkr2[R2], u2[R2];
-#pragma unroll
-      for (int i2 = 0; i2 < R2; ++i2) {
-        k2[i2] = pack2(kr[2 * i2], kr[2 * i2 + 1]);
-        gkr2[i2] = 0ull;
-        u2[i2] = 0ull;
-      }
-      // undo the update, r = k.G (column partial), gk partial = G ins (row partial)
-      u64 ary[C], arq[C], ark[C];
-#pragma unroll
-      for (int j = 0; j < C; ++j) {
-        const u64 iy = dup2(beta[0] * dyc[j]);
-        const u64 iq = dup2(beta[1] * dqc[j]);
-        const u64 ik = dup2(beta[2] * dkc[j]);
-        ary[j] = 0ull; arq[j] = 0ull; ark[j] = 0ull;
+      u64 k2[R2], gkr2[R2];
+      {
+        float kr[R];
+        ld_vec<R>(sk + t * E + rg * R, kr);
 #pragma unroll
         for (int i2 = 0; i2 < R2; ++i2) {
-          const u64 nk = neg2(k2[i2]);
-          Wy[i2][j] = fma2<PK>(nk, iy, Wy[i2][j]);
-          Wq[i2][j] = fma2<PK>(nk, iq, Wq[i2][j]);
-          Wk[i2][j] = fma2<PK>(nk, ik, Wk[i2][j]);
-          ary[j] = fma2<PK>(k2[i2], Gy[i2][j], ary[j]);
-          arq[j] = fma2<PK>(k2[i2], Gq[i2][j], arq[j]);
-          ark[j] = fma2<PK>(k2[i2], Gk[i2][j], ark[j]);
-          gkr2[i2] = fma2<PK>(Gy[i2][j], iy, gkr2[i2]);
-          gkr2[i2] = fma2<PK>(Gq[i2][j], iq, gkr2[i2]);
-          gkr2[i2] = fma2<PK>(Gk[i2][j], ik, gkr2[i2]);
+          k2[i2] = pack2(kr[2 * i2], kr[2 * i2 + 1]);
+          gkr2[i2] = 0ull;
         }
       }
+      // per block: undo the update, r = k.G (column partial), gk partial += G ins (row partial)
+      float rcol[3][C];
+      auto blk1 = [&](u64 (&W)[R2][C], u64 (&G)[R2][C], const float* sd, float bz, float (&rz)[C]) {
+        float dz[C];
+        ld_vec<C>(sd + t * E + cg * C, dz);
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+          const u64 ins = dup2(bz * dz[j]);
+          u64 ar = 0ull;
+#pragma unroll
+          for (int i2 = 0; i2 < R2; ++i2) {
+            W[i2][j] = fma2<PK>(neg2(k2[i2]), ins, W[i2][j]);
+            ar = fma2<PK>(k2[i2], G[i2][j], ar);
+            gkr2[i2] = fma2<PK>(G[i2][j], ins, gkr2[i2]);
+          }
+          rz[j] = hsum2(ar);
+        }
+      };
+      blk1(Wy, Gy, syd, beta[0], rcol[0]);
+      blk1(Wq, Gq, sqd, beta[1], rcol[1]);
+      blk1(Wk, Gk, skd, beta[2], rcol[2]);
       float gkr[R], ur[R];
 #pragma unroll
       for (int i2 = 0; i2 < R2; ++i2) unpack2(gkr2[i2], gkr[2 * i2], gkr[2 * i2 + 1]);
-      // w_b column of this column group
-      float rb = 0.f, insb = 0.f;
-      float wr[R], gr[R];
+      // w_b column jb: same three operations on shared-memory state
+      float rb = 0.f, bdj = 0.f;
       if (jb >= 0) {
-        insb = beta[3] * bdv[jb];
+        float kr[R], wr[R], gr[R];
+        ld_vec<R>(sk + t * E + rg * R, kr);
         ld_vec<R>(wbT + jb * E + rg * R, wr);
         ld_vec<R>(gbT + jb * E + rg * R, gr);
+        bdj = sbd[t * 4 + jb];
+        const float insb = beta[3] * bdj;
 #pragma unroll
         for (int i = 0; i < R; ++i) {
           wr[i] = fmaf(-kr[i], insb, wr[i]);
           rb = fmaf(kr[i], gr[i], rb);
           gkr[i] = fmaf(gr[i], insb, gkr[i]);
         }
+        st_vec<R>(wbT + jb * E + rg * R, wr);
       }
       // complete r over the row groups; gd = b r; scalar partials r.d
-      float gdy[C], gdq[C], gdk[C];
-      float sb0 = 0.f, sb1 = 0.f, sb2 = 0.f, sb3 = 0.f;
+      float sc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int j = 0; j < C; ++j) {
-        const float ry = allreduce_rows<NRG>(hsum2(ary[j]));
-        const float rq = allreduce_rows<NRG>(hsum2(arq[j]));
-        const float rk = allreduce_rows<NRG>(hsum2(ark[j]));
-        gdy[j] = beta[0] * ry;
-        gdq[j] = beta[1] * rq;
-        gdk[j] = beta[2] * rk;
-        sb0 = fmaf(ry, dyc[j], sb0);
-        sb1 = fmaf(rq, dqc[j], sb1);
-        sb2 = fmaf(rk, dkc[j], sb2);
-      }
-      rb = allreduce_rows<NRG>(rb);
-      float gdb = 0.f;
-      if (jb >= 0) {
-        gdb = beta[3] * rb;
-        sb3 = rb * bdv[jb];
-      }
-      if (rg != 0) { sb0 = 0.f; sb1 = 0.f; sb2 = 0.f; sb3 = 0.f; }   // one lane per column group counts
-      // G += (q-k)^T gd ; u = W(t-1) gd (row partial)
+      for (int z = 0; z < 3; ++z) {
+        float dz[C];
+        ld_vec<C>((z == 0 ? syd : (z == 1 ? sqd : skd)) + t * E + cg * C, dz);
 #pragma unroll
-      for (int j = 0; j < C; ++j) {
-        const u64 gy2 = dup2(gdy[j]);
-        const u64 gq2 = dup2(gdq[j]);
-        const u64 gk2 = dup2(gdk[j]);
-#pragma unroll
-        for (int i2 = 0; i2 < R2; ++i2) {
-          const u64 d2 = pack2(qr[2 * i2] - kr[2 * i2], qr[2 * i2 + 1] - kr[2 * i2 + 1]);
-          Gy[i2][j] = fma2<PK>(d2, gy2, Gy[i2][j]);
-          Gq[i2][j] = fma2<PK>(d2, gq2, Gq[i2][j]);
-          Gk[i2][j] = fma2<PK>(d2, gk2, Gk[i2][j]);
-          u2[i2] = fma2<PK>(Wy[i2][j], gy2, u2[i2]);
-          u2[i2] = fma2<PK>(Wq[i2][j], gq2, u2[i2]);
-          u2[i2] = fma2<PK>(Wk[i2][j], gk2, u2[i2]);
+        for (int j = 0; j < C; ++j) {
+          const float r = allreduce_rows<NRG>(rcol[z][j]);
+          sc8[z] = fmaf(r, dz[j], sc8[z]);
+          rcol[z][j] = beta[z] * r;   // now gd
         }
       }
+      rb = allreduce_rows<NRG>(rb);
+      const float gdb = beta[3] * rb;
+      sc8[3] = rb * bdj;
+      if (rg != 0) { sc8[0] = 0.f; sc8[1] = 0.f; sc8[2] = 0.f; sc8[3] = 0.f; }   // count each column once
+      // G += (q-k)^T gd ; u = W(t-1) gd (row partial)
+      u64 d2[R2], u2[R2];
+      {
+        float kr[R], qr[R];
+        ld_vec<R>(sk + t * E + rg * R, kr);
+        ld_vec<R>(sq + t * E + rg * R, qr);
+#pragma unroll
+        for (int i2 = 0; i2 < R2; ++i2) {
+          d2[i2] = pack2(qr[2 * i2] - kr[2 * i2], qr[2 * i2 + 1] - kr[2 * i2 + 1]);
+          u2[i2] = 0ull;
+        }
+      }
+      auto blk2 = [&](u64 (&W)[R2][C], u64 (&G)[R2][C], const float (&gd)[C]) {
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+          const u64 g2 = dup2(gd[j]);
+#pragma unroll
+          for (int i2 = 0; i2 < R2; ++i2) {
+            G[i2][j] = fma2<PK>(d2[i2], g2, G[i2][j]);
+            u2[i2] = fma2<PK>(W[i2][j], g2, u2[i2]);
+          }
+        }
+      };
+      blk2(Wy, Gy, rcol[0]);
+      blk2(Wq, Gq, rcol[1]);
+      blk2(Wk, Gk, rcol[2]);
 #pragma unroll
       for (int i2 = 0; i2 < R2; ++i2) unpack2(u2[i2], ur[2 * i2], ur[2 * i2 + 1]);
       if (jb >= 0) {
+        float wr[R], gr[R];
+        ld_vec<R>(wbT + jb * E + rg * R, wr);
+        ld_vec<R>(gbT + jb * E + rg * R, gr);
 #pragma unroll
-        for (int i = 0; i < R; ++i) {
-          gr[i] = fmaf(qr[i] - kr[i], gdb, gr[i]);
-          ur[i] = fmaf(wr[i], gdb, ur[i]);
+        for (int i2 = 0; i2 < R2; ++i2) {
+          float da, db;
+          unpack2(d2[i2], da, db);
+          gr[2 * i2] = fmaf(da, gdb, gr[2 * i2]);
+          gr[2 * i2 + 1] = fmaf(db, gdb, gr[2 * i2 + 1]);
+          ur[2 * i2] = fmaf(wr[2 * i2], gdb, ur[2 * i2]);
+          ur[2 * i2 + 1] = fmaf(wr[2 * i2 + 1], gdb, ur[2 * i2 + 1]);
         }
+        st_vec<R>(gbT + jb * E + rg * R, gr);
       }
       // row partials: gq = u, gk = G ins - u ; their dot products with q, k
-      float dotq = 0.f, dotk = 0.f;
+      {
+        float kr[R], qr[R];
+        ld_vec<R>(sk + t * E + rg * R, kr);
+        ld_vec<R>(sq + t * E + rg * R, qr);
 #pragma unroll
-      for (int i = 0; i < R; ++i) {
-        gkr[i] -= ur[i];
-        dotq = fmaf(qr[i], ur[i], dotq);
-        dotk = fmaf(kr[i], gkr[i], dotk);
+        for (int i = 0; i < R; ++i) {
+          gkr[i] -= ur[i];
+          sc8[4] = fmaf(qr[i], ur[i], sc8[4]);
+          sc8[5] = fmaf(kr[i], gkr[i], sc8[5]);
+        }
       }
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        ur[i] = allreduce_cols<NRG>(ur[i]);
-        gkr[i] = allreduce_cols<NRG>(gkr[i]);
-      }
-      sb0 = allreduce_warp(sb0);
-      sb1 = allreduce_warp(sb1);
-      sb2 = allreduce_warp(sb2);
-      sb3 = allreduce_warp(sb3);
-      dotq = allreduce_warp(dotq);
-      dotk = allreduce_warp(dotk);
       float* xr_cur = xrow + (par * NWARP + warp) * 2 * E;
       float* xs_cur = xsc + (par * NWARP + warp) * 8;
-      if (lane < NRG) {
-        st_vec<R>(xr_cur + rg * R, ur);
-        st_vec<R>(xr_cur + E + rg * R, gkr);
-      }
-      if (lane == 0) {
-        float sc[8] = {sb0, sb1, sb2, sb3, dotq, dotk, 0.f, 0.f};
-        st_vec<8>(xs_cur, sc);
+      if constexpr (SCATTER) {
+        float v[2 * R];
+#pragma unroll
+        for (int i = 0; i < R; ++i) { v[i] = ur[i]; v[R + i] = gkr[i]; }
+        reduce_scatter<2 * R, CGW, NRG>(v, lane);
+        float piece[S_ROW];
+#pragma unroll
+        for (int i = 0; i < S_ROW; ++i) piece[i] = v[i];
+        // lanes of the lower half of the column groups hold pieces of u, the upper half of gk
+        const int which = cgl >= CGW / 2 ? 1 : 0;
+        st_vec<S_ROW>(xr_cur + which * E + rg * R + (cgl % (CGW / 2)) * S_ROW, piece);
+        reduce_scatter<8, NRG, 1>(sc8, lane);
+        float sp[S_SC];
+#pragma unroll
+        for (int i = 0; i < S_SC; ++i) sp[i] = allreduce_cols<NRG>(sc8[i]);
+        if (cgl == 0) st_vec<S_SC>(xs_cur + rg * S_SC, sp);
+      } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          ur[i] = allreduce_cols<NRG>(ur[i]);
+          gkr[i] = allreduce_cols<NRG>(gkr[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) sc8[i] = allreduce_warp(sc8[i]);
+        if (lane < NRG) {
+          st_vec<R>(xr_cur + rg * R, ur);
+          st_vec<R>(xr_cur + E + rg * R, gkr);
+        }
+        if (lane == 0) st_vec<8>(xs_cur, sc8);
       }
       __syncthreads();
 
@@ -535,19 +808,27 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       for (int i = 0; i < 8; ++i) sc[i] = 0.f;
 #pragma unroll
       for (int w = 0; w < NWARP; ++w) {
-        float a[C], b[C], s[8];
+        float a[C], b[C], s8[8];
         ld_vec<C>(xrow + (par * NWARP + w) * 2 * E + cg * C, a);
         ld_vec<C>(xrow + (par * NWARP + w) * 2 * E + E + cg * C, b);
-        ld_vec<8>(xsc + (par * NWARP + w) * 8, s);
+        ld_vec<8>(xsc + (par * NWARP + w) * 8, s8);
 #pragma unroll
         for (int j = 0; j < C; ++j) { gqc[j] += a[j]; gkc[j] += b[j]; }
 #pragma unroll
-        for (int i = 0; i < 6; ++i) sc[i] += s[i];
+        for (int i = 0; i < 6; ++i) sc[i] += s8[i];
       }
-      float qc[C], kc[C], gc[C];
-      ld_vec<C>(sq + t * E + cg * C, qc);
-      ld_vec<C>(sk + t * E + cg * C, kc);
-      ld_vec<C>(sg + t * E + cg * C, gc);
+      float pre[3][C];
+      {
+        float qc[C], kc[C];
+        ld_vec<C>(sq + t * E + cg * C, qc);
+        ld_vec<C>(sk + t * E + cg * C, kc);
+        ld_vec<C>(sg + t * E + cg * C, pre[0]);
+#pragma unroll
+        for (int j = 0; j < C; ++j) {
+          pre[1][j] = qc[j] * (gqc[j] - sc[4]);
+          pre[2][j] = kc[j] * (gkc[j] - sc[5]);
+        }
+      }
       float xr[R];
       ld_vec<R>(sx + t * E + rg * R, xr);
       u64 gx2[R2], x2[R2];
@@ -556,25 +837,27 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         gx2[i2] = 0ull;
         x2[i2] = pack2(xr[2 * i2], xr[2 * i2 + 1]);
       }
+      auto blk3 = [&](u64 (&W)[R2][C], u64 (&G)[R2][C], const float (&pz)[C]) {
 #pragma unroll
-      for (int j = 0; j < C; ++j) {
-        const u64 py = dup2(gc[j]);
-        const u64 pq = dup2(qc[j] * (gqc[j] - sc[4]));
-        const u64 pk = dup2(kc[j] * (gkc[j] - sc[5]));
+        for (int j = 0; j < C; ++j) {
+          const u64 pd = dup2(pz[j]);
 #pragma unroll
-        for (int i2 = 0; i2 < R2; ++i2) {
-          gx2[i2] = fma2<PK>(Wy[i2][j], py, gx2[i2]);
-          gx2[i2] = fma2<PK>(Wq[i2][j], pq, gx2[i2]);
-          gx2[i2] = fma2<PK>(Wk[i2][j], pk, gx2[i2]);
-          Gy[i2][j] = fma2<PK>(x2[i2], py, Gy[i2][j]);
-          Gq[i2][j] = fma2<PK>(x2[i2], pq, Gq[i2][j]);
-          Gk[i2][j] = fma2<PK>(x2[i2], pk, Gk[i2][j]);
+          for (int i2 = 0; i2 < R2; ++i2) {
+            gx2[i2] = fma2<PK>(W[i2][j], pd, gx2[i2]);
+            G[i2][j] = fma2<PK>(x2[i2], pd, G[i2][j]);
+          }
         }
-      }
+      };
+      blk3(Wy, Gy, pre[0]);
+      blk3(Wq, Gq, pre[1]);
+      blk3(Wk, Gk, pre[2]);
       float gxr[R];
 #pragma unroll
       for (int i2 = 0; i2 < R2; ++i2) unpack2(gx2[i2], gxr[2 * i2], gxr[2 * i2 + 1]);
       if (jb >= 0) {
+        float wr[R], gr[R];
+        ld_vec<R>(wbT + jb * E + rg * R, wr);
+        ld_vec<R>(gbT + jb * E + rg * R, gr);
         const float b = beta[jb];
         const float pb = sc[jb] * b * (1.f - b);
 #pragma unroll
@@ -582,12 +865,19 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
           gxr[i] = fmaf(wr[i], pb, gxr[i]);
           gr[i] = fmaf(xr[i], pb, gr[i]);
         }
-        st_vec<R>(wbT + jb * E + rg * R, wr);
         st_vec<R>(gbT + jb * E + rg * R, gr);
       }
+      if constexpr (SCATTER) {
+        reduce_scatter<R, CGW, NRG>(gxr, lane);
+        float piece[S_GX];
 #pragma unroll
-      for (int i = 0; i < R; ++i) gxr[i] = allreduce_cols<NRG>(gxr[i]);
-      if (lane < NRG) st_vec<R>(sgx + (t * NWARP + warp) * E + rg * R, gxr);
+        for (int i = 0; i < S_GX; ++i) piece[i] = gxr[i];
+        st_vec<S_GX>(sgx + (t * NWARP + warp) * E + rg * R + cgl * S_GX, piece);
+      } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) gxr[i] = allreduce_cols<NRG>(gxr[i]);
+        if (lane < NRG) st_vec<R>(sgx + (t * NWARP + warp) * E + rg * R, gxr);
+      }
     }
 
     __syncthreads();
