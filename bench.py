@@ -45,9 +45,10 @@ WORKLOADS = {
     "srwm_c1": dict(op="srwm", B=4, H=4, L=64, E=16, dtype="f32"),
     "delta_c2": dict(op="delta", B=32, H=8, L=512, E=64, dtype="f32"),
     "srwm_c3op": dict(op="srwm", B=128, H=16, L=128, E=32, dtype="f32"),
-    # small cases for profiler captures (saved activations still exceed the 126 MB L2)
-    "srwm_prof": dict(op="srwm", B=32, H=16, L=512, E=64, dtype="bf16"),
-    "delta_prof": dict(op="delta", B=32, H=16, L=1024, E=64, dtype="bf16"),
+    # small cases for profiler captures (saved activations still exceed the 126 MB L2,
+    # and the grid is a whole number of waves: 592 = 148 SMs x 4, 1184 = 148 x 8)
+    "srwm_prof": dict(op="srwm", B=37, H=16, L=512, E=64, dtype="bf16"),
+    "delta_prof": dict(op="delta", B=74, H=16, L=1024, E=64, dtype="bf16"),
 }
 
 # CPU sample sizes for the host baseline (same H, E, dtype=fp32 math; fewer sequences/steps)

@@ -18,17 +18,22 @@
   X(64, 2, 128, 16, 16, true, 3) \
   X(64, 3, 128, 8, 16, false, 3)
 
-// Column-layout forward (96 threads): Y(E, variant, T, PK, MINB, DPRE)
+// Column-layout forward (96 threads, one warp per block): Y(E, variant, T, PK, MINB, DPRE, NRP)
 //   DPRE  the k warp publishes q-k once per step (two-warp named barrier) instead of every
 //         thread recomputing it in the second pass
-#define SRWM_FWD_COL_CONFIGS(Y)  \
-  Y(64, 0, 16, true, 4, false)   \
-  Y(64, 4, 16, true, 3, false)   \
-  Y(64, 5, 16, false, 4, false)  \
-  Y(64, 6, 16, true, 4, true)    \
-  Y(32, 0, 16, true, 8, false)   \
-  Y(32, 4, 16, true, 12, false)  \
-  Y(32, 5, 16, true, 8, true)
+//   NRP   row parts per column group (1 = whole columns per lane)
+#define SRWM_FWD_COL_CONFIGS(Y)     \
+  Y(64, 0, 16, true, 4, true, 1)    \
+  Y(64, 4, 16, true, 4, false, 1)   \
+  Y(64, 5, 16, true, 4, true, 2)    \
+  Y(64, 6, 16, true, 4, true, 4)    \
+  Y(64, 7, 16, false, 4, true, 2)   \
+  Y(64, 8, 16, true, 3, true, 2)    \
+  Y(32, 0, 16, true, 8, true, 1)    \
+  Y(32, 4, 16, true, 8, false, 1)   \
+  Y(32, 5, 16, true, 8, true, 2)    \
+  Y(32, 6, 16, true, 8, true, 4)    \
+  Y(32, 7, 16, true, 12, true, 4)
 
 #define SRWM_BWD_CONFIGS(X)      \
   X(8, 0, 32, 2, 16, true, 8)    \

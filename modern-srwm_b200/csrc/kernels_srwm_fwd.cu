@@ -21,13 +21,13 @@ int run(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int 
   return launch_kernel(srwm_fwd_kernel<TIO, E, P, R, T, PK, MINB>, p, grid, P, smem, s, &dev_mask, cuda_err);
 }
 
-template <int E, int T, bool PK, int MINB, bool DPRE>
+template <int E, int T, bool PK, int MINB, bool DPRE, int NRP>
 int run_col(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
   constexpr int smem = SrwmFwdColSmem<TIO, E, T>::TOTAL;
-  if (info) { info->P = 96; info->R = E; info->T = T; info->smem = smem; }
+  if (info) { info->P = 96; info->R = E / NRP; info->T = T; info->smem = smem; }
   if (describe_only) return 0;
   static unsigned long long dev_mask = 0;
-  return launch_kernel(srwm_fwd_col_kernel<TIO, E, T, PK, MINB, DPRE>, p, grid, 96, smem, s, &dev_mask, cuda_err);
+  return launch_kernel(srwm_fwd_col_kernel<TIO, E, T, PK, MINB, DPRE, NRP>, p, grid, 96, smem, s, &dev_mask, cuda_err);
 }
 
 }  // namespace
@@ -43,8 +43,8 @@ int dispatch_srwm_fwd_f32(
   if (E == E_ && variant == V_) return run<E_, P_, R_, T_, PK_, MINB_>(p, grid, s, info, describe_only, cuda_err);
   SRWM_FWD_CONFIGS(X)
 #undef X
-#define Y(E_, V_, T_, PK_, MINB_, DPRE_) \
-  if (E == E_ && variant == V_) return run_col<E_, T_, PK_, MINB_, DPRE_>(p, grid, s, info, describe_only, cuda_err);
+#define Y(E_, V_, T_, PK_, MINB_, DPRE_, NRP_) \
+  if (E == E_ && variant == V_) return run_col<E_, T_, PK_, MINB_, DPRE_, NRP_>(p, grid, s, info, describe_only, cuda_err);
   SRWM_FWD_COL_CONFIGS(Y)
 #undef Y
   return (E == 8 || E == 16 || E == 32 || E == 64) ? -6 : -3;

@@ -305,14 +305,20 @@ __device__ __forceinline__ float warp_max(float v) {
   return r;
 }
 
-template <typename TIO, int E, int T, bool PK, int MINB, bool DPRE>
+template <typename TIO, int E, int T, bool PK, int MINB, bool DPRE, int NRP>
 __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdParams p) {
   static_assert(E == 32 || E == 64, "column layout needs a whole warp of columns per block");
+  // Lane (cq, rp) of a warp holds CPL adjacent columns x RL rows (row part rp of NRP) of the
+  // warp's block.  NRP = 1 is the pure column layout; NRP > 1 trades a log2(NRP)-stage
+  // shuffle per pass for 1/NRP of the broadcast operand loads (the shared-memory data pipe
+  // is the busiest unit of this kernel).
   using SM = SrwmFwdColSmem<TIO, E, T>;
-  constexpr int P = 96, CPL = E / 32, E2 = E / 2, RB = E / 8;
+  constexpr int P = 96, CPL = (E / 32) * NRP, RL = E / NRP, RL2 = RL / 2, VPL = CPL / NRP, RB = E / 8;
+  static_assert(NRP == 1 || NRP == 2 || NRP == 4, "row parts per column group");
+  static_assert(RL % 4 == 0 && CPL % NRP == 0, "bad column-layout shape");
   const int tid = threadIdx.x;
   const int warp = tid / 32, lane = tid % 32;
-  const int c0 = lane * CPL;
+  const int rp = lane % NRP, c0 = (lane / NRP) * CPL;
   const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
   const bool save = !(p.flags & 1u);
   const int jb = lane / 8, r8 = lane % 8;   // warp 0: w_b column / row eighth of this lane
@@ -332,14 +338,14 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
   float* sdq = wbT + 4 * E;     // [2][E]  q - k of the current step (DPRE)
   float* sdz = warp == 0 ? syd : (warp == 1 ? sqd : skd);
 
-  u64 W[E2][CPL];
+  u64 W[RL2][CPL];
   float* gW = (warp == 0 ? p.Wy : (warp == 1 ? p.Wq : p.Wk)).mat(n, h);
   float* gwb = p.wb.mat(n, h);
 #pragma unroll
-  for (int e2 = 0; e2 < E2; ++e2) {
+  for (int e2 = 0; e2 < RL2; ++e2) {
     float a[CPL], b[CPL];
-    ld_vec<CPL>(gW + (2 * e2) * E + c0, a);
-    ld_vec<CPL>(gW + (2 * e2 + 1) * E + c0, b);
+    ld_vec<CPL>(gW + (rp * RL + 2 * e2) * E + c0, a);
+    ld_vec<CPL>(gW + (rp * RL + 2 * e2 + 1) * E + c0, b);
 #pragma unroll
     for (int c = 0; c < CPL; ++c) W[e2][c] = pack2(a[c], b[c]);
   }
@@ -382,13 +388,13 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       const float* qr = sq + t * E;
       const float* kr = sk + t * E;
       float* dq = sdq + par * E;
-      // ---- pass 1: this lane's columns of x.W ---------------------------------------------
+      // ---- pass 1: this lane's part of x.W --------------------------------------------------
       u64 a0[CPL], a1[CPL];
 #pragma unroll
       for (int cc = 0; cc < CPL; ++cc) { a0[cc] = 0ull; a1[cc] = 0ull; }
 #pragma unroll
-      for (int e4 = 0; e4 < E / 4; ++e4) {
-        const float4 xv = reinterpret_cast<const float4*>(xr)[e4];
+      for (int e4 = 0; e4 < RL / 4; ++e4) {
+        const float4 xv = reinterpret_cast<const float4*>(xr + rp * RL)[e4];
         const u64 p0 = pack2(xv.x, xv.y), p1 = pack2(xv.z, xv.w);
 #pragma unroll
         for (int cc = 0; cc < CPL; ++cc) {
@@ -399,8 +405,13 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       float v[CPL];
 #pragma unroll
       for (int cc = 0; cc < CPL; ++cc) v[cc] = hsum2(a0[cc]) + hsum2(a1[cc]);
+      reduce_scatter<CPL, NRP, 1>(v, lane);   // lane rp keeps columns c0 + rp*VPL .. + VPL
+      float vs[VPL];
+#pragma unroll
+      for (int i = 0; i < VPL; ++i) vs[i] = v[i];
+      const int cs = c0 + rp * VPL;
       if (warp == 0) {
-        st_vec<CPL>(sy + t * E + c0, v);
+        st_vec<VPL>(sy + t * E + cs, vs);
         float xrow[RB], wrow[RB];
         ld_vec<RB>(xr + r8 * RB, xrow);
         ld_vec<RB>(wbT + jb * E + r8 * RB, wrow);
@@ -410,28 +421,28 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
         pb = allreduce_rows<8>(pb);
         if (r8 == 0) sbeta[t * 4 + jb] = fast_sigmoid(pb);
       } else {
-        float m = v[0];
+        float m = vs[0];
 #pragma unroll
-        for (int cc = 1; cc < CPL; ++cc) m = fmaxf(m, v[cc]);
+        for (int i = 1; i < VPL; ++i) m = fmaxf(m, vs[i]);
         m = warp_max(m);
         float ssum = 0.f;
 #pragma unroll
-        for (int cc = 0; cc < CPL; ++cc) { v[cc] = __expf(v[cc] - m); ssum += v[cc]; }
+        for (int i = 0; i < VPL; ++i) { vs[i] = __expf(vs[i] - m); ssum += vs[i]; }
         ssum = allreduce_warp(ssum);
         const float inv = __fdividef(1.f, ssum);
 #pragma unroll
-        for (int cc = 0; cc < CPL; ++cc) v[cc] *= inv;
-        st_vec<CPL>((warp == 1 ? sq : sk) + t * E + c0, v);
+        for (int i = 0; i < VPL; ++i) vs[i] *= inv;
+        st_vec<VPL>((warp == 1 ? sq : sk) + t * E + cs, vs);
         if constexpr (DPRE) {
           // the k warp publishes q - k once for everybody: it needs q from the q warp,
           // handed over through a two-warp named barrier
           asm volatile("bar.sync 1, 64;" ::: "memory");
           if (warp == 2) {
-            float qv[CPL];
-            ld_vec<CPL>(qr + c0, qv);
+            float qv[VPL];
+            ld_vec<VPL>(qr + cs, qv);
 #pragma unroll
-            for (int cc = 0; cc < CPL; ++cc) qv[cc] -= v[cc];
-            st_vec<CPL>(dq + c0, qv);
+            for (int i = 0; i < VPL; ++i) qv[i] -= vs[i];
+            st_vec<VPL>(dq + cs, qv);
           }
         }
       }
@@ -441,15 +452,15 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
 #pragma unroll
       for (int cc = 0; cc < CPL; ++cc) { a0[cc] = 0ull; a1[cc] = 0ull; }
 #pragma unroll
-      for (int e4 = 0; e4 < E / 4; ++e4) {
+      for (int e4 = 0; e4 < RL / 4; ++e4) {
         u64 d0, d1;
         if constexpr (DPRE) {
-          const float4 dv = reinterpret_cast<const float4*>(dq)[e4];
+          const float4 dv = reinterpret_cast<const float4*>(dq + rp * RL)[e4];
           d0 = pack2(dv.x, dv.y);
           d1 = pack2(dv.z, dv.w);
         } else {
-          const float4 qv = reinterpret_cast<const float4*>(qr)[e4];
-          const float4 kv = reinterpret_cast<const float4*>(kr)[e4];
+          const float4 qv = reinterpret_cast<const float4*>(qr + rp * RL)[e4];
+          const float4 kv = reinterpret_cast<const float4*>(kr + rp * RL)[e4];
           d0 = fma2<PK>(pack2(kv.x, kv.y), neg1, pack2(qv.x, qv.y));
           d1 = fma2<PK>(pack2(kv.z, kv.w), neg1, pack2(qv.z, qv.w));
         }
@@ -463,10 +474,10 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       u64 ins2[CPL];
 #pragma unroll
       for (int cc = 0; cc < CPL; ++cc) {
-        v[cc] = hsum2(a0[cc]) + hsum2(a1[cc]);
+        v[cc] = allreduce_rows<NRP>(hsum2(a0[cc]) + hsum2(a1[cc]));
         ins2[cc] = dup2(bz * v[cc]);
       }
-      st_vec<CPL>(sdz + t * E + c0, v);
+      if (rp == 0) st_vec<CPL>(sdz + t * E + c0, v);
       if (warp == 0) {   // w_b column jb, rows of this lane
         float qrow[RB], krow[RB], wrow[RB];
         ld_vec<RB>(qr + r8 * RB, qrow);
@@ -484,8 +495,8 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       }
       // ---- rank-1 update -------------------------------------------------------------------
 #pragma unroll
-      for (int e4 = 0; e4 < E / 4; ++e4) {
-        const float4 kv = reinterpret_cast<const float4*>(kr)[e4];
+      for (int e4 = 0; e4 < RL / 4; ++e4) {
+        const float4 kv = reinterpret_cast<const float4*>(kr + rp * RL)[e4];
         const u64 k0 = pack2(kv.x, kv.y), k1 = pack2(kv.z, kv.w);
 #pragma unroll
         for (int cc = 0; cc < CPL; ++cc) {
@@ -509,12 +520,12 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
   }
 
 #pragma unroll
-  for (int e2 = 0; e2 < E2; ++e2) {
+  for (int e2 = 0; e2 < RL2; ++e2) {
     float a[CPL], b[CPL];
 #pragma unroll
     for (int cc = 0; cc < CPL; ++cc) unpack2(W[e2][cc], a[cc], b[cc]);
-    st_vec<CPL>(gW + (2 * e2) * E + c0, a);
-    st_vec<CPL>(gW + (2 * e2 + 1) * E + c0, b);
+    st_vec<CPL>(gW + (rp * RL + 2 * e2) * E + c0, a);
+    st_vec<CPL>(gW + (rp * RL + 2 * e2 + 1) * E + c0, b);
   }
   __syncthreads();
   for (int i = tid; i < 4 * E; i += P) gwb[i] = wbT[(i % 4) * E + i / 4];
