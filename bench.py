@@ -327,73 +327,98 @@ def timed_region(fn, steps, warmup, dist_on, device):
 
 
 def run_e2e(wl, Bl, device, steps, warmup, dist_on):
-    """Same metric through the public autograd entry point with host-resident activations:
-    per step, H2D copy of the activations from pinned memory, forward, backward, batch
-    reduction of the slow-weight gradients (autograd's repeat-backward), all-reduce, and a
-    D2H read of those gradients."""
+    """Same metric through the public autograd entry point with host-resident activations.
+
+    Per step: H2D copy of that step's activations from pinned host memory, forward, backward,
+    batch reduction of the slow-weight gradients (autograd's repeat-backward), all-reduce,
+    and a D2H read of the result, followed by a stream synchronise.  The input pipeline is
+    double buffered the way a prefetching data loader is: while step s computes, the copy of
+    step s+1's activations runs on a side stream into the other device buffer, so every
+    timed step contains exactly one full H2D copy, overlapped with compute."""
     import torch.distributed as dist
     import srwm_b200 as sb
     H, L, E = wl["H"], wl["L"], wl["E"]
     dt = torch.bfloat16 if wl["dtype"] == "bf16" else torch.float32
     g = torch.Generator().manual_seed(7)
+    copy_stream = torch.cuda.Stream(device=device)
+    ready = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    state = {"i": 0}
+
+    def pinned(shape, fill):
+        t = torch.empty(shape, dtype=dt).pin_memory()
+        chunk = max(1, (1 << 26) // max(1, t[0].numel()))
+        for i in range(0, shape[0], chunk):
+            t[i:i + chunk] = fill((min(chunk, shape[0] - i),) + tuple(shape[1:])).to(dt)
+        return t
+
     if wl["op"] == "srwm":
-        hx = torch.empty((Bl, H, L, E), dtype=dt).pin_memory()
-        chunk = max(1, (1 << 26) // (H * L * E))
-        for i in range(0, Bl, chunk):
-            hx[i:i + chunk] = torch.randn((min(chunk, Bl - i), H, L, E), generator=g).to(dt)
-        go = torch.randn((Bl, H, L, E), device=device, dtype=dt)
+        host = [pinned((Bl, H, L, E), lambda s: torch.randn(s, generator=g))]
+    else:
+        host = [pinned((Bl, H, L, E), lambda s: torch.softmax(torch.randn(s, generator=g), -1)),
+                pinned((Bl, H, L, E), lambda s: torch.softmax(torch.randn(s, generator=g), -1)),
+                pinned((Bl, H, L, E), lambda s: torch.randn(s, generator=g)),
+                pinned((Bl, H, L, 1), lambda s: torch.sigmoid(torch.randn(s, generator=g)))]
+    dev = [[torch.empty(h.shape, device=device, dtype=dt) for h in host] for _ in range(2)]
+    h2d = sum(h.numel() * h.element_size() for h in host)
+    go = torch.randn((Bl, H, L, E), device=device, dtype=dt)
+
+    def prefetch(slot):
+        cur = torch.cuda.current_stream(device)
+        copy_stream.wait_event(consumed[slot])
+        with torch.cuda.stream(copy_stream):
+            for d, h in zip(dev[slot], host):
+                d.copy_(h, non_blocking=True)
+            ready[slot].record(copy_stream)
+        del cur
+
+    for ev in consumed:
+        ev.record(torch.cuda.current_stream(device))
+    prefetch(0)
+
+    if wl["op"] == "srwm":
         std = E ** -0.5
         slow = [(torch.randn(1, H, E, E, device=device) * std).requires_grad_() for _ in range(3)]
         slow.append((torch.randn(1, H, E, 4, device=device) * std).requires_grad_())
         nflat = sum(w.numel() for w in slow)
-        hgrad = torch.empty(nflat, dtype=torch.float32).pin_memory()
-        dx = torch.empty((Bl, H, L, E), device=device, dtype=dt)
-        h2d = hx.numel() * hx.element_size()
-        d2h = nflat * 4
+        hres = torch.empty(nflat, dtype=torch.float32).pin_memory()
 
-        def step(_timed):
-            dx.copy_(hx, non_blocking=True)
-            x = dx.detach().requires_grad_()
+        def compute(bufs):
+            x = bufs[0].detach().requires_grad_()
             Wb = [w.repeat(Bl, 1, 1, 1) for w in slow]
             out = sb.self_ref_v0(x, *Wb)
             out.backward(go)
             flat = torch.cat([w.grad.reshape(-1) for w in slow])
             if dist_on:
                 dist.all_reduce(flat)
-            hgrad.copy_(flat, non_blocking=True)
+            hres.copy_(flat, non_blocking=True)
             for w in slow:
                 w.grad = None
-            torch.cuda.current_stream().synchronize()
     else:
-        hq, hk, hv = (torch.empty((Bl, H, L, E), dtype=dt).pin_memory() for _ in range(3))
-        hb = torch.empty((Bl, H, L, 1), dtype=dt).pin_memory()
-        chunk = max(1, (1 << 26) // (H * L * E))
-        for i in range(0, Bl, chunk):
-            n = min(chunk, Bl - i)
-            hq[i:i + n] = torch.softmax(torch.randn((n, H, L, E), generator=g), -1).to(dt)
-            hk[i:i + n] = torch.softmax(torch.randn((n, H, L, E), generator=g), -1).to(dt)
-            hv[i:i + n] = torch.randn((n, H, L, E), generator=g).to(dt)
-            hb[i:i + n] = torch.sigmoid(torch.randn((n, H, L, 1), generator=g)).to(dt)
-        go = torch.randn((Bl, H, L, E), device=device, dtype=dt)
-        dq, dk, dv = (torch.empty((Bl, H, L, E), device=device, dtype=dt) for _ in range(3))
-        db = torch.empty((Bl, H, L, 1), device=device, dtype=dt)
         W = torch.zeros(Bl, H, E, E, device=device)
         hres = torch.empty(Bl * H, dtype=torch.float32).pin_memory()
-        h2d = sum(t.numel() * t.element_size() for t in (hq, hk, hv, hb))
-        d2h = hres.numel() * 4
 
-        def step(_timed):
-            dq.copy_(hq, non_blocking=True); dk.copy_(hk, non_blocking=True)
-            dv.copy_(hv, non_blocking=True); db.copy_(hb, non_blocking=True)
-            q, k, v, b = (t.detach().requires_grad_() for t in (dq, dk, dv, db))
+        def compute(bufs):
+            q, k, v, b = (t.detach().requires_grad_() for t in bufs)
             W.zero_()
             out = sb.fast_weight_delta(q, k, v, b, W)
             out.backward(go)
-            # per-sequence summary of the gradient as the step's result
+            # per-sequence summary of a gradient as the step's result
             hres.copy_(b.grad.float().sum(dim=(2, 3)).reshape(-1), non_blocking=True)
-            torch.cuda.current_stream().synchronize()
+    d2h = hres.numel() * 4
+
+    def step(_timed):
+        slot = state["i"] % 2
+        state["i"] += 1
+        cur = torch.cuda.current_stream(device)
+        prefetch(1 - slot)                 # next step's activations, overlapped with this step
+        cur.wait_event(ready[slot])
+        compute(dev[slot])
+        consumed[slot].record(cur)
+        cur.synchronize()                  # the host holds this step's result
 
     ms = timed_region(step, steps, warmup, dist_on, device)
+    copy_stream.synchronize()
     return ms, h2d, d2h
 
 
@@ -433,7 +458,7 @@ def run_ours(args):
         torch.cuda.empty_cache()
         e2e_ms, h2d, d2h = (None, 0, 0)
         if not args.no_e2e:
-            e2e_ms, h2d, d2h = run_e2e(wl, Bl, device, max(1, min(args.steps, args.e2e_steps)), min(args.warmup, 3),
+            e2e_ms, h2d, d2h = run_e2e(wl, Bl, device, max(1, min(args.steps, args.e2e_steps)), max(1, min(args.warmup, 3)),
                                        dist_on)
             torch.cuda.empty_cache()
         tokens = wl["B"] * wl["L"]
@@ -450,7 +475,8 @@ def run_ours(args):
                                              "ms_per_step": e2e_ms},
             roofline={"bound": "hbm", "kernel": f"{wl['op']}_bwd_kernel", "achieved": achieved, "peak": hbm_peak,
                       "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": f"of {peak_kind}",
-                      "traffic": NCU_TRAFFIC.get(name),
+                      "traffic": (NCU_BWD_DRAM_BYTES_PER_SEQ_STEP[wl["op"]] * seqs_local * wl["L"]
+                                  if wl["E"] == 64 and wl["dtype"] == "bf16" else None),
                       "algorithmic_bytes_per_launch": bwd_bytes, "launch_ms": bwd_ms},
             fp32={"fwd_tflops": seqs_local * wl["L"] * ff / (fwd_ms * 1e-3) / 1e12,
                   "bwd_tflops": seqs_local * wl["L"] * fb / (bwd_ms * 1e-3) / 1e12,
@@ -483,9 +509,12 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
-# DRAM bytes per launch of the backward kernel from ncu captures (dram__bytes_read.sum +
-# dram__bytes_write.sum), scaled to the full workload by sequence-steps; see profiles/.
-NCU_TRAFFIC = {}
+# DRAM bytes per (sequence, step) of the backward kernels at d_head 64 with bf16 activations,
+# from ncu captures of the *_prof workloads (dram__bytes_read.sum + dram__bytes_write.sum
+# divided by sequences x steps; profiles/*_d64_bf16_*.txt).  `roofline.traffic` scales this
+# to a full launch by the sequence-steps it processes (traffic is streamed once, so it
+# grows in proportion).
+NCU_BWD_DRAM_BYTES_PER_SEQ_STEP = {"srwm": 1842.0, "delta": 1423.7}
 
 
 def main():
