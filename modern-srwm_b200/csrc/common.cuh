@@ -167,6 +167,62 @@ __device__ __forceinline__ void st_vec(__nv_bfloat16* p, const float (&v)[N]) {
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Row mapping of a tile.  A thread's R local rows are not one contiguous run: local row i
+// of row group rg is global row
+//     (i/4) * (4*NRG) + rg*4 + i%4          (R a multiple of 4)
+// i.e. quads of 4 consecutive rows, quad q of all row groups side by side.  The lanes of a
+// column group then read a row vector (k, q, x ...) from shared memory as 16-byte pieces
+// at a 16-byte stride -- bank-conflict free -- instead of at a 4*R-byte stride.
+// ---------------------------------------------------------------------------------------
+template <int R, int NRG>
+__device__ __forceinline__ int row_of(int rg, int i) {
+  if constexpr (R % 4 == 0) return (i / 4) * (4 * NRG) + rg * 4 + (i % 4);
+  else return rg * R + i;
+}
+template <int R, int NRG, typename T>
+__device__ __forceinline__ void ld_rows(const T* base, int rg, float (&v)[R]) {
+  if constexpr (R % 4 == 0) {
+#pragma unroll
+    for (int q = 0; q < R / 4; ++q) {
+      float t[4];
+      ld_vec<4>(base + q * 4 * NRG + rg * 4, t);
+      v[4 * q] = t[0]; v[4 * q + 1] = t[1]; v[4 * q + 2] = t[2]; v[4 * q + 3] = t[3];
+    }
+  } else {
+    ld_vec<R>(base + rg * R, v);
+  }
+}
+// store S consecutive local rows starting at local row i0 (S <= 4 stays inside one quad)
+template <int S, int R, int NRG, int NV>
+__device__ __forceinline__ void st_rows_piece(float* base, int rg, int i0, const float (&v)[NV]) {
+  static_assert(S <= NV, "piece larger than its source");
+  if constexpr (R % 4 == 0) {
+    if constexpr (S <= 4) {
+      float t[S];
+#pragma unroll
+      for (int i = 0; i < S; ++i) t[i] = v[i];
+      st_vec<S>(base + (i0 / 4) * (4 * NRG) + rg * 4 + (i0 % 4), t);
+    } else {
+      static_assert(S % 4 == 0, "pieces longer than a quad are whole quads");
+#pragma unroll
+      for (int q = 0; q < S / 4; ++q) {
+        float t[4] = {v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]};
+        st_vec<4>(base + (i0 / 4 + q) * (4 * NRG) + rg * 4, t);
+      }
+    }
+  } else {
+    float t[S];
+#pragma unroll
+    for (int i = 0; i < S; ++i) t[i] = v[i];
+    st_vec<S>(base + rg * R + i0, t);
+  }
+}
+template <int R, int NRG>
+__device__ __forceinline__ void st_rows(float* base, int rg, const float (&v)[R]) {
+  st_rows_piece<R, R, NRG>(base, rg, 0, v);
+}
+
 __device__ __forceinline__ float to_f32(float v) { return v; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
 __device__ __forceinline__ void from_f32(float& d, float v) { d = v; }

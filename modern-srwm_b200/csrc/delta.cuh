@@ -58,8 +58,8 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
 #pragma unroll
   for (int i2 = 0; i2 < R2; ++i2) {
     float a[C], b[C];
-    ld_vec<C>(Wg + (rg * R + 2 * i2) * E + cg * C, a);
-    ld_vec<C>(Wg + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+    ld_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
+    ld_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
 #pragma unroll
     for (int j = 0; j < C; ++j) W[i2][j] = pack2(a[j], b[j]);
   }
@@ -108,8 +108,8 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
 
     for (int t = 0; t < nt; ++t) {
       float kr[R], qr[R], vc[C];
-      ld_vec<R>(sk + t * E + rg * R, kr);
-      ld_vec<R>(sq + t * E + rg * R, qr);
+      ld_rows<R, NRG>(sk + t * E, rg, kr);
+      ld_rows<R, NRG>(sq + t * E, rg, qr);
       ld_vec<C>(sv + t * E + cg * C, vc);
       const float bt = sb[t];
 
@@ -175,8 +175,8 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
     float a[C], b[C];
 #pragma unroll
     for (int j = 0; j < C; ++j) unpack2(W[i2][j], a[j], b[j]);
-    st_vec<C>(Wg + (rg * R + 2 * i2) * E + cg * C, a);
-    st_vec<C>(Wg + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+    st_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
+    st_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
   }
 }
 
@@ -208,10 +208,14 @@ template <typename TIO, int E, int P, int R, int T, bool PK, int MINB>
 __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams p) {
   using TL = Tiling<E, P, R>;
   using SM = DeltaBwdSmem<TIO, E, P, T>;
-  constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2, NWARP = TL::NWARP;
+  constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2, NWARP = TL::NWARP, CGW = TL::CGW;
+  // row sums leave the warp through a reduce-scatter when the tile shape allows it
+  constexpr bool SCATTER = (CGW >= 2) && ((2 * R) % CGW == 0) && ((2 * R) / CGW <= 4 || ((2 * R) / CGW) % 4 == 0);
+  constexpr int S_ROW = SCATTER ? (2 * R) / CGW : R;
   const int tid = threadIdx.x;
   const int rg = tid % NRG, cg = tid / NRG;
   const int warp = tid / 32, lane = tid % 32;
+  const int cgl = lane / NRG;
   const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
 
   extern __shared__ __align__(16) unsigned char smem[];
@@ -225,8 +229,8 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
 #pragma unroll
   for (int i2 = 0; i2 < R2; ++i2) {
     float a[C], b[C];
-    ld_vec<C>(Wg + (rg * R + 2 * i2) * E + cg * C, a);
-    ld_vec<C>(Wg + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+    ld_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
+    ld_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
 #pragma unroll
     for (int j = 0; j < C; ++j) { W[i2][j] = pack2(a[j], b[j]); G[i2][j] = 0ull; }
   }
@@ -287,8 +291,8 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
 
     for (int t = nt - 1; t >= 0; --t) {
       float kr[R], qr[R], gc[C], insc[C], vc[C], voc[C];
-      ld_vec<R>(sk + t * E + rg * R, kr);
-      ld_vec<R>(sq + t * E + rg * R, qr);
+      ld_rows<R, NRG>(sk + t * E, rg, kr);
+      ld_rows<R, NRG>(sq + t * E, rg, qr);
       ld_vec<C>(sg + t * E + cg * C, gc);
       ld_vec<C>(svi + t * E + cg * C, insc);
       ld_vec<C>(sv + t * E + cg * C, vc);
@@ -344,18 +348,27 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
         unpack2(gq2[i2], gqr[2 * i2], gqr[2 * i2 + 1]);
         unpack2(gk2[i2], gkr[2 * i2], gkr[2 * i2 + 1]);
       }
-#pragma unroll
-      for (int i = 0; i < R; ++i) {
-        gqr[i] = allreduce_cols<NRG>(gqr[i]);
-        gkr[i] = allreduce_cols<NRG>(gkr[i]);
-      }
       gb = allreduce_cols<NRG>(rg == 0 ? gb : 0.f);
-      if (lane < NRG) {   // column group 0 of the warp: lane == rg
-        float* dst = spart + ((t * NWARP + warp) * 2) * E + rg * R;
-        st_vec<R>(dst, gqr);
-        st_vec<R>(dst + E, gkr);
-        if (lane == 0) sgb[t * NWARP + warp] = gb;
+      float* part = spart + ((t * NWARP + warp) * 2) * E;
+      if constexpr (SCATTER) {
+        float v[2 * R];
+#pragma unroll
+        for (int i = 0; i < R; ++i) { v[i] = gqr[i]; v[R + i] = gkr[i]; }
+        reduce_scatter<2 * R, CGW, NRG>(v, lane);
+        const int which = cgl >= CGW / 2 ? 1 : 0;   // lower half of the column groups: gq pieces, upper: gk
+        st_rows_piece<S_ROW, R, NRG>(part + which * E, rg, (cgl % (CGW / 2)) * S_ROW, v);
+      } else {
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          gqr[i] = allreduce_cols<NRG>(gqr[i]);
+          gkr[i] = allreduce_cols<NRG>(gkr[i]);
+        }
+        if (lane < NRG) {   // column group 0 of the warp: lane == rg
+          st_rows<R, NRG>(part, rg, gqr);
+          st_rows<R, NRG>(part + E, rg, gkr);
+        }
       }
+      if (lane == 0) sgb[t * NWARP + warp] = gb;
     }
 
     if (has_next) {
@@ -397,8 +410,8 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
     float a[C], b[C];
 #pragma unroll
     for (int j = 0; j < C; ++j) unpack2(W[i2][j], a[j], b[j]);
-    st_vec<C>(Wg + (rg * R + 2 * i2) * E + cg * C, a);
-    st_vec<C>(Wg + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+    st_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
+    st_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
   }
   if (p.gW0.base != nullptr) {
     float* Gg = p.gW0.mat(n, h);
@@ -407,8 +420,8 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
       float a[C], b[C];
 #pragma unroll
       for (int j = 0; j < C; ++j) unpack2(G[i2][j], a[j], b[j]);
-      st_vec<C>(Gg + (rg * R + 2 * i2) * E + cg * C, a);
-      st_vec<C>(Gg + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+      st_vec<C>(Gg + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
+      st_vec<C>(Gg + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
     }
   }
 }

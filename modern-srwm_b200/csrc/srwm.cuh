@@ -38,8 +38,8 @@ __device__ __forceinline__ void load_tile(const float* g, int rg, int cg, u64 (&
 #pragma unroll
   for (int i2 = 0; i2 < R / 2; ++i2) {
     float a[C], b[C];
-    ld_vec<C>(g + (rg * R + 2 * i2) * E + cg * C, a);
-    ld_vec<C>(g + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+    ld_vec<C>(g + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
+    ld_vec<C>(g + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
 #pragma unroll
     for (int j = 0; j < C; ++j) W[i2][j] = pack2(a[j], b[j]);
   }
@@ -51,8 +51,8 @@ __device__ __forceinline__ void store_tile(float* g, int rg, int cg, const u64 (
     float a[C], b[C];
 #pragma unroll
     for (int j = 0; j < C; ++j) unpack2(W[i2][j], a[j], b[j]);
-    st_vec<C>(g + (rg * R + 2 * i2) * E + cg * C, a);
-    st_vec<C>(g + (rg * R + 2 * i2 + 1) * E + cg * C, b);
+    st_vec<C>(g + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
+    st_vec<C>(g + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
   }
 }
 
@@ -128,7 +128,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
     for (int t = 0; t < nt; ++t, par ^= 1) {
       // ---- pass 1: [y, q~, k~, b~] = x.W ------------------------------------------------
       float xr[R];
-      ld_vec<R>(sx + t * E + rg * R, xr);
+      ld_rows<R, NRG>(sx + t * E, rg, xr);
       u64 ay[C], aq[C], ak[C];
 #pragma unroll
       for (int j = 0; j < C; ++j) { ay[j] = 0ull; aq[j] = 0ull; ak[j] = 0ull; }
@@ -145,7 +145,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
       float pb = 0.f;
       if (jb >= 0) {
         float wr[R];
-        ld_vec<R>(wbT + jb * E + rg * R, wr);
+        ld_rows<R, NRG>(wbT + jb * E, rg, wr);
 #pragma unroll
         for (int i = 0; i < R; ++i) pb = fmaf(xr[i], wr[i], pb);
       }
@@ -172,8 +172,8 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
 
       // ---- softmax of q~ and k~ on this thread's rows ------------------------------------
       float qr[R], kr[R];
-      ld_vec<R>(xq_cur + rg * R, qr);
-      ld_vec<R>(xq_cur + E + rg * R, kr);
+      ld_rows<R, NRG>(xq_cur, rg, qr);
+      ld_rows<R, NRG>(xq_cur + E, rg, kr);
       float mq = qr[0], mk = kr[0];
 #pragma unroll
       for (int i = 1; i < R; ++i) { mq = fmaxf(mq, qr[i]); mk = fmaxf(mk, kr[i]); }
@@ -193,8 +193,8 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
 #pragma unroll
       for (int i = 0; i < R; ++i) { qr[i] *= iq; kr[i] *= ik; }
       if (save && cg == 0) {
-        st_vec<R>(sq + t * E + rg * R, qr);
-        st_vec<R>(sk + t * E + rg * R, kr);
+        st_rows<R, NRG>(sq + t * E, rg, qr);
+        st_rows<R, NRG>(sk + t * E, rg, kr);
       }
       float beta[4];
       ld_vec<4>(xbeta + par * 4, beta);
@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
       float db = 0.f;
       float wr[R];
       if (jb >= 0) {
-        ld_vec<R>(wbT + jb * E + rg * R, wr);
+        ld_rows<R, NRG>(wbT + jb * E, rg, wr);
 #pragma unroll
         for (int i = 0; i < R; ++i) db = fmaf(qr[i] - kr[i], wr[i], db);
       }
@@ -253,7 +253,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
         const float ib = beta[3] * db;
 #pragma unroll
         for (int i = 0; i < R; ++i) wr[i] = fmaf(kr[i], ib, wr[i]);
-        st_vec<R>(wbT + jb * E + rg * R, wr);   // only this thread ever touches these entries
+        st_rows<R, NRG>(wbT + jb * E, rg, wr);   // only this thread ever touches these entries
       }
     }
 
@@ -657,7 +657,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       u64 k2[R2], gkr2[R2];
       {
         float kr[R];
-        ld_vec<R>(sk + t * E + rg * R, kr);
+        ld_rows<R, NRG>(sk + t * E, rg, kr);
 #pragma unroll
         for (int i2 = 0; i2 < R2; ++i2) {
           k2[i2] = pack2(kr[2 * i2], kr[2 * i2 + 1]);
@@ -692,9 +692,9 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       float rb = 0.f, bdj = 0.f;
       if (jb >= 0) {
         float kr[R], wr[R], gr[R];
-        ld_vec<R>(sk + t * E + rg * R, kr);
-        ld_vec<R>(wbT + jb * E + rg * R, wr);
-        ld_vec<R>(gbT + jb * E + rg * R, gr);
+        ld_rows<R, NRG>(sk + t * E, rg, kr);
+        ld_rows<R, NRG>(wbT + jb * E, rg, wr);
+        ld_rows<R, NRG>(gbT + jb * E, rg, gr);
         bdj = sbd[t * 4 + jb];
         const float insb = beta[3] * bdj;
 #pragma unroll
@@ -703,7 +703,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
           rb = fmaf(kr[i], gr[i], rb);
           gkr[i] = fmaf(gr[i], insb, gkr[i]);
         }
-        st_vec<R>(wbT + jb * E + rg * R, wr);
+        st_rows<R, NRG>(wbT + jb * E, rg, wr);
       }
       // complete r over the row groups; gd = b r; scalar partials r.d
       float sc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
@@ -726,8 +726,8 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       u64 d2[R2], u2[R2];
       {
         float kr[R], qr[R];
-        ld_vec<R>(sk + t * E + rg * R, kr);
-        ld_vec<R>(sq + t * E + rg * R, qr);
+        ld_rows<R, NRG>(sk + t * E, rg, kr);
+        ld_rows<R, NRG>(sq + t * E, rg, qr);
 #pragma unroll
         for (int i2 = 0; i2 < R2; ++i2) {
           d2[i2] = pack2(qr[2 * i2] - kr[2 * i2], qr[2 * i2 + 1] - kr[2 * i2 + 1]);
@@ -752,8 +752,8 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       for (int i2 = 0; i2 < R2; ++i2) unpack2(u2[i2], ur[2 * i2], ur[2 * i2 + 1]);
       if (jb >= 0) {
         float wr[R], gr[R];
-        ld_vec<R>(wbT + jb * E + rg * R, wr);
-        ld_vec<R>(gbT + jb * E + rg * R, gr);
+        ld_rows<R, NRG>(wbT + jb * E, rg, wr);
+        ld_rows<R, NRG>(gbT + jb * E, rg, gr);
 #pragma unroll
         for (int i2 = 0; i2 < R2; ++i2) {
           float da, db;
@@ -763,13 +763,13 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
           ur[2 * i2] = fmaf(wr[2 * i2], gdb, ur[2 * i2]);
           ur[2 * i2 + 1] = fmaf(wr[2 * i2 + 1], gdb, ur[2 * i2 + 1]);
         }
-        st_vec<R>(gbT + jb * E + rg * R, gr);
+        st_rows<R, NRG>(gbT + jb * E, rg, gr);
       }
       // row partials: gq = u, gk = G ins - u ; their dot products with q, k
       {
         float kr[R], qr[R];
-        ld_vec<R>(sk + t * E + rg * R, kr);
-        ld_vec<R>(sq + t * E + rg * R, qr);
+        ld_rows<R, NRG>(sk + t * E, rg, kr);
+        ld_rows<R, NRG>(sq + t * E, rg, qr);
 #pragma unroll
         for (int i = 0; i < R; ++i) {
           gkr[i] -= ur[i];
@@ -789,7 +789,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         for (int i = 0; i < S_ROW; ++i) piece[i] = v[i];
         // lanes of the lower half of the column groups hold pieces of u, the upper half of gk
         const int which = cgl >= CGW / 2 ? 1 : 0;
-        st_vec<S_ROW>(xr_cur + which * E + rg * R + (cgl % (CGW / 2)) * S_ROW, piece);
+        st_rows_piece<S_ROW, R, NRG>(xr_cur + which * E, rg, (cgl % (CGW / 2)) * S_ROW, piece);
         reduce_scatter<8, NRG, 1>(sc8, lane);
         float sp[S_SC];
 #pragma unroll
@@ -804,8 +804,8 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
 #pragma unroll
         for (int i = 0; i < 8; ++i) sc8[i] = allreduce_warp(sc8[i]);
         if (lane < NRG) {
-          st_vec<R>(xr_cur + rg * R, ur);
-          st_vec<R>(xr_cur + E + rg * R, gkr);
+          st_rows<R, NRG>(xr_cur, rg, ur);
+          st_rows<R, NRG>(xr_cur + E, rg, gkr);
         }
         if (lane == 0) st_vec<8>(xs_cur, sc8);
       }
@@ -841,7 +841,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         }
       }
       float xr[R];
-      ld_vec<R>(sx + t * E + rg * R, xr);
+      ld_rows<R, NRG>(sx + t * E, rg, xr);
       u64 gx2[R2], x2[R2];
 #pragma unroll
       for (int i2 = 0; i2 < R2; ++i2) {
@@ -867,8 +867,8 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       for (int i2 = 0; i2 < R2; ++i2) unpack2(gx2[i2], gxr[2 * i2], gxr[2 * i2 + 1]);
       if (jb >= 0) {
         float wr[R], gr[R];
-        ld_vec<R>(wbT + jb * E + rg * R, wr);
-        ld_vec<R>(gbT + jb * E + rg * R, gr);
+        ld_rows<R, NRG>(wbT + jb * E, rg, wr);
+        ld_rows<R, NRG>(gbT + jb * E, rg, gr);
         const float b = beta[jb];
         const float pb = sc[jb] * b * (1.f - b);
 #pragma unroll
@@ -876,18 +876,18 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
           gxr[i] = fmaf(wr[i], pb, gxr[i]);
           gr[i] = fmaf(xr[i], pb, gr[i]);
         }
-        st_vec<R>(gbT + jb * E + rg * R, gr);
+        st_rows<R, NRG>(gbT + jb * E, rg, gr);
       }
       if constexpr (SCATTER) {
         reduce_scatter<R, CGW, NRG>(gxr, lane);
         float piece[S_GX];
 #pragma unroll
         for (int i = 0; i < S_GX; ++i) piece[i] = gxr[i];
-        st_vec<S_GX>(sgx + (t * NWARP + warp) * E + rg * R + cgl * S_GX, piece);
+        st_rows_piece<S_GX, R, NRG>(sgx + (t * NWARP + warp) * E, rg, cgl * S_GX, piece);
       } else {
 #pragma unroll
         for (int i = 0; i < R; ++i) gxr[i] = allreduce_cols<NRG>(gxr[i]);
-        if (lane < NRG) st_vec<R>(sgx + (t * NWARP + warp) * E + rg * R, gxr);
+        if (lane < NRG) st_rows<R, NRG>(sgx + (t * NWARP + warp) * E, rg, gxr);
       }
     }
 
