@@ -671,13 +671,13 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         ld_vec<C>(sd + t * E + cg * C, dz);
 #pragma unroll
         for (int j = 0; j < C; ++j) {
-          const u64 ins = dup2(bz * dz[j]);
+          const u64 nins = dup2(-bz * dz[j]);   // minus the inserted value: undoes the update; gkr2 collects -G.ins
           u64 ar = 0ull;
 #pragma unroll
           for (int i2 = 0; i2 < R2; ++i2) {
-            W[i2][j] = fma2<PK>(neg2(k2[i2]), ins, W[i2][j]);
+            W[i2][j] = fma2<PK>(k2[i2], nins, W[i2][j]);
             ar = fma2<PK>(k2[i2], G[i2][j], ar);
-            gkr2[i2] = fma2<PK>(G[i2][j], ins, gkr2[i2]);
+            gkr2[i2] = fma2<PK>(G[i2][j], nins, gkr2[i2]);
           }
           rz[j] = hsum2(ar);
         }
@@ -685,7 +685,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       blk1(Wy, Gy, syd, beta[0], rcol[0]);
       blk1(Wq, Gq, sqd, beta[1], rcol[1]);
       blk1(Wk, Gk, skd, beta[2], rcol[2]);
-      float gkr[R], ur[R];
+      float gkr[R], ur[R];   // gkr holds MINUS the row partial of G.ins until the subtraction of u below
 #pragma unroll
       for (int i2 = 0; i2 < R2; ++i2) unpack2(gkr2[i2], gkr[2 * i2], gkr[2 * i2 + 1]);
       // w_b column jb: same three operations on shared-memory state
@@ -701,7 +701,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         for (int i = 0; i < R; ++i) {
           wr[i] = fmaf(-kr[i], insb, wr[i]);
           rb = fmaf(kr[i], gr[i], rb);
-          gkr[i] = fmaf(gr[i], insb, gkr[i]);
+          gkr[i] = fmaf(-gr[i], insb, gkr[i]);
         }
         st_rows<R, NRG>(wbT + jb * E, rg, wr);
       }
@@ -772,7 +772,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         ld_rows<R, NRG>(sq + t * E, rg, qr);
 #pragma unroll
         for (int i = 0; i < R; ++i) {
-          gkr[i] -= ur[i];
+          gkr[i] = -gkr[i] - ur[i];
           sc8[4] = fmaf(qr[i], ur[i], sc8[4]);
           sc8[5] = fmaf(kr[i], gkr[i], sc8[5]);
         }
@@ -869,7 +869,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         float wr[R], gr[R];
         ld_rows<R, NRG>(wbT + jb * E, rg, wr);
         ld_rows<R, NRG>(gbT + jb * E, rg, gr);
-        const float b = beta[jb];
+        const float b = sbeta[t * 4 + jb];
         const float pb = sc[jb] * b * (1.f - b);
 #pragma unroll
         for (int i = 0; i < R; ++i) {
