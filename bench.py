@@ -45,6 +45,7 @@ WORKLOADS = {
     "srwm_c1": dict(op="srwm", B=4, H=4, L=64, E=16, dtype="f32"),
     "delta_c2": dict(op="delta", B=32, H=8, L=512, E=64, dtype="f32"),
     "srwm_c3op": dict(op="srwm", B=128, H=16, L=128, E=32, dtype="f32"),
+    "srwm_c4_learner": dict(op="srwm", B=32, H=8, L=100, E=32, dtype="f32"),
     # small cases for profiler captures (saved activations still exceed the 126 MB L2,
     # and the grid is a whole number of waves: 592 = 148 SMs x 4, 1184 = 148 x 8)
     "srwm_prof": dict(op="srwm", B=37, H=16, L=512, E=64, dtype="bf16"),
@@ -517,6 +518,46 @@ def run_ours(args):
 NCU_BWD_DRAM_BYTES_PER_SEQ_STEP = {"srwm": 1842.0, "delta": 1423.7}
 
 
+def run_table(args):
+    """Operator-level fwd+bwd timings of every configuration (one JSON line each), plus the
+    RL actor path: single-step forward calls (L=1, B=48, H=8, d=32) with the state carried,
+    through the public entry point under no_grad."""
+    import srwm_b200 as sb
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    for name in ("srwm_c1", "delta_c2", "srwm_c3op", "srwm_c4_learner", "srwm_c5", "delta_c5"):
+        wl = WORKLOADS[name]
+        ob = OpBench(wl, wl["B"], device, seed=1)
+        ms = timed_region(ob.step, args.steps, args.warmup, False, device)
+        f, b = ob.kernel_ms()
+        ff, fb = algorithmic_flops(wl["op"], wl["E"])
+        seqs = wl["B"] * wl["H"]
+        print(json.dumps({"workload": name, "config": config_of(name, wl, 1)["workload"], "ms_per_step": ms,
+                          "tokens_per_s": wl["B"] * wl["L"] / (ms * 1e-3), "fwd_ms": f, "bwd_ms": b,
+                          "fwd_tflops": seqs * wl["L"] * ff / (f * 1e-3) / 1e12,
+                          "bwd_tflops": seqs * wl["L"] * fb / (b * 1e-3) / 1e12}), flush=True)
+        del ob
+        torch.cuda.empty_cache()
+    # actor path
+    B, H, E = 48, 8, 32
+    g = torch.Generator(device=device).manual_seed(3)
+    x = torch.softmax(torch.randn(B, H, 1, E, device=device, generator=g), -1)
+    std = E ** -0.5
+    W = [torch.randn(B, H, E, E, device=device, generator=g) * std for _ in range(3)]
+    W.append(torch.randn(B, H, E, 4, device=device, generator=g) * std)
+
+    def actor(_timed):
+        with torch.no_grad():
+            for _ in range(100):
+                sb.self_ref_v0(x, *W)
+
+    ms = timed_region(actor, args.steps, args.warmup, False, device)
+    print(json.dumps({"workload": "srwm_c4_actor", "config": "SRWM forward only, L=1 B=48 H=8 d=32, state carried, "
+                      "100 consecutive calls per step through self_ref_v0 under no_grad",
+                      "ms_per_100_calls": ms, "us_per_call": ms * 10.0, "env_steps_per_s": 100 * B / (ms * 1e-3)}),
+          flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -528,8 +569,11 @@ def main():
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--table", action="store_true", help="operator-level timings of every configuration")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.table:
+        run_table(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)
