@@ -106,6 +106,8 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
     const TIO* sv = reinterpret_cast<const TIO*>(ib + 2 * T * SM::ROW_IO);
     const float* sb = beta_buf(c & 1);
 
+    #pragma unroll 1
+
     for (int t = 0; t < nt; ++t) {
       float kr[R], qr[R], vc[C];
       ld_rows<R, NRG>(sk + t * E, rg, kr);
@@ -288,6 +290,8 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
     const float* svo = reinterpret_cast<const float*>(ib + 4 * T * SM::ROW_IO);
     const float* svi = svo + T * E;
     const float* sb = beta_buf(c & 1);
+
+    #pragma unroll 1
 
     for (int t = nt - 1; t >= 0; --t) {
       float kr[R], qr[R], gc[C], insc[C], vc[C], voc[C];

@@ -125,6 +125,8 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
     __syncthreads();   // chunk c (and, first time, w_b) visible; output stage free again
     const TIO* sx = in_buf(c & 1);
 
+    #pragma unroll 1
+
     for (int t = 0; t < nt; ++t, par ^= 1) {
       // ---- pass 1: [y, q~, k~, b~] = x.W ------------------------------------------------
       float xr[R];
@@ -382,6 +384,8 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       __syncthreads();
       sxf = xf32;
     }
+
+    #pragma unroll 1
 
     for (int t = 0; t < nt; ++t, par ^= 1) {
       const float* xr = sxf + t * E;
@@ -649,6 +653,8 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
     const float* skd = sqd + T * E;
     const float* sbeta = skd + T * E;
     const float* sbd = sbeta + T * 4;
+
+    #pragma unroll 1
 
     for (int t = nt - 1; t >= 0; --t, par ^= 1) {
       // ================= phase 1 =================
