@@ -123,6 +123,25 @@ def _state_desc(t):
     return L.State(t.data_ptr(), s[0], s[1])
 
 
+def _like(t, last=None):
+    """Uninitialised tensor with the shape of ``t`` (optionally another last dimension) laid
+    out in memory like ``t``.  The layers hand in permuted views of ``[L, B, H*d]``
+    activations (supervised_learning/layer.py:161-165) and turn the result back with
+    ``transpose(1, 2).reshape(B, L, H*d)`` (:184-186); when the output follows the input's
+    memory order that reshape is a view instead of a full copy, and the same holds for the
+    gradients on the way back."""
+    if last is None or last == t.size(-1):
+        return torch.empty_like(t)      # preserve_format keeps the strides of a dense permuted view
+    shape = tuple(t.shape[:-1]) + (last,)
+    order = sorted(range(3), key=lambda d: (-t.stride(d), d))      # outer-to-inner memory order
+    strides = [0, 0, 0, 1]
+    run = last
+    for d in reversed(order):
+        strides[d] = run
+        run *= shape[d]
+    return torch.empty_strided(shape, strides, device=t.device, dtype=t.dtype)
+
+
 _NULL_SEQ = L.Seq(None, 0, 0, 0)
 _NULL_STATE = L.State(None, 0, 0)
 
@@ -163,7 +182,7 @@ def srwm_forward(x, W_y, W_q, W_k, w_b, save=True, variant=None):
     xs = _seq(x.detach())
     st = _StateIO(W_y, W_q, W_k, w_b)
     dev = x.device
-    out = torch.empty((N, H, Ln, E), device=dev, dtype=x.dtype)
+    out = _like(xs)
     a = L.SrwmFwdArgs()
     a.N, a.H, a.L, a.E = N, H, Ln, E
     a.io_dtype = dt
@@ -209,7 +228,7 @@ def srwm_backward(x, saved, grad_out, W_y, W_q, W_k, w_b, grad_state=None, resto
     go = _seq(go)
     st = _StateIO(W_y, W_q, W_k, w_b)
     dev = x.device
-    grad_x = torch.empty((N, H, Ln, E), device=dev, dtype=x.dtype)
+    grad_x = _like(xs)
     flags = 0
     if grad_state is not None and any(g is not None for g in grad_state):
         shapes = [(N, H, E, E)] * 3 + [(N, H, E, 4)]
@@ -254,7 +273,7 @@ def delta_forward(Q, K, V, beta, W, save=True, variant=None):
     bs = beta.detach().to(Q.dtype)
     st = _StateIO(W)
     dev = Q.device
-    out = torch.empty((N, H, Ln, M), device=dev, dtype=Q.dtype)
+    out = _like(Qs, M)
     a = L.DeltaFwdArgs()
     a.N, a.H, a.L, a.E, a.M = N, H, Ln, E, M
     a.io_dtype = dt
@@ -290,9 +309,9 @@ def delta_backward(Q, K, V, beta, saved, grad_out, W, want_grad_W0=False, varian
     go = _seq(grad_out.detach().to(Q.dtype))
     st = _StateIO(W)
     dev = Q.device
-    gQ = torch.empty((N, H, Ln, E), device=dev, dtype=Q.dtype)
-    gK = torch.empty((N, H, Ln, E), device=dev, dtype=Q.dtype)
-    gV = torch.empty((N, H, Ln, M), device=dev, dtype=Q.dtype)
+    gQ = _like(Qs)
+    gK = _like(Ks)
+    gV = _like(Qs, M)
     gB = torch.empty((N, H, Ln, 1), device=dev, dtype=Q.dtype)
     gW0 = torch.empty((N, H, E, M), device=dev, dtype=torch.float32) if want_grad_W0 else None
     a = L.DeltaBwdArgs()

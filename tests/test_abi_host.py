@@ -151,3 +151,20 @@ def test_variant_env_parsing(monkeypatch):
     assert ops._variant("srwm_bwd", 64) == 1 and ops._variant("delta_fwd", 32) == 1
     assert ops._variant("srwm_fwd", 64) == 0
     ops._variants.clear()
+
+
+def test_outputs_follow_the_memory_order_of_the_input_view():
+    # layer-style view of a [L, B, H*d] activation: the result laid out the same way turns the
+    # layer's transpose(1, 2).reshape(B, L, H*d) into a view (no copy)
+    L_, B_, H_, d_ = 7, 3, 4, 16
+    h = torch.zeros(L_, B_, H_ * d_)
+    x = h.reshape(L_, B_, H_, d_).permute(1, 2, 0, 3)
+    out = ops._like(x)
+    assert out.shape == x.shape and out.stride() == x.stride()
+    back = out.transpose(1, 2).reshape(B_, L_, H_ * d_)
+    assert back.data_ptr() == out.data_ptr()                 # a view, not a copy
+    assert back.transpose(0, 1).is_contiguous()
+    o2 = ops._like(x, 8)
+    assert o2.shape == (B_, H_, L_, 8) and o2.stride() == (H_ * 8, 8, B_ * H_ * 8, 1)
+    c = torch.zeros(B_, H_, L_, d_)
+    assert ops._like(c).is_contiguous() and ops._like(c, 4).is_contiguous()

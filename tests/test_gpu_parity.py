@@ -455,3 +455,33 @@ def test_full_size_sweep_config_subset():
         assert orc.rel_max(grads[0][n:n + 1, h:h + 1].float().cpu(), r[0]) < BF16_TOL
         for t, o in zip(grads[1:], r[1:5]):
             assert orc.rel_max(t[n:n + 1, h:h + 1].cpu(), o) < GRAD_TOL
+
+
+def test_layer_style_call_needs_no_layout_copies():
+    # x as the SRWM layer passes it (supervised_learning/layer.py:161-165): the output comes
+    # back in the same memory order, so the layer's transpose+reshape is a view
+    sb = _sb()
+    d = _dev()
+    L_, B_, H_, E = 23, 3, 4, 32
+    g = torch.Generator().manual_seed(77)
+    h = torch.randn(L_, B_, H_ * E, generator=g)
+    slow = [torch.randn(1, H_, E, E, generator=g) * E ** -0.5 for _ in range(3)] + [torch.randn(1, H_, E, 4, generator=g) * E ** -0.5]
+    hd = h.to(d).requires_grad_()
+    x = hd.reshape(L_, B_, H_, E).permute(1, 2, 0, 3)
+    sd = [w.to(d).requires_grad_() for w in slow]
+    out = sb.self_ref_v0(x, *[w.repeat(B_, 1, 1, 1) for w in sd])
+    assert out.stride() == x.stride()
+    back = out.transpose(1, 2).reshape(B_, L_, H_ * E)
+    assert back.data_ptr() == out.data_ptr()
+    y = back.transpose(0, 1)
+    go = torch.randn(L_, B_, H_ * E, generator=g)
+    (y * go.to(d)).sum().backward()
+    hr = h.double().requires_grad_()
+    sr = [w.double().requires_grad_() for w in slow]
+    ref, _ = orc.srwm_loop(hr.reshape(L_, B_, H_, E).permute(1, 2, 0, 3), *[w.repeat(B_, 1, 1, 1) for w in sr])
+    yr = ref.transpose(1, 2).reshape(B_, L_, H_ * E).transpose(0, 1)
+    (yr * go.double()).sum().backward()
+    assert orc.rel_max(y.detach().cpu(), yr.detach()) < FWD_TOL
+    assert orc.rel_max(hd.grad.cpu(), hr.grad) < GRAD_TOL
+    for a, b in zip(sd, sr):
+        assert orc.rel_max(a.grad.cpu(), b.grad) < GRAD_TOL
