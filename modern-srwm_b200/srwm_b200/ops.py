@@ -80,12 +80,13 @@ def _require_cuda(*ts):
 def _seq_ok(t):
     """innermost contiguous and every row 16-byte aligned (strides of size-1 dims ignored)."""
     es = t.element_size()
-    if t.size(-1) > 1 and t.stride(-1) != 1:
+    sh, st = t.shape, t.stride()
+    if sh[3] > 1 and st[3] != 1:
         return False
     if t.data_ptr() % 16:
         return False
     for d in range(3):
-        if t.size(d) > 1 and (t.stride(d) * es) % 16:
+        if sh[d] > 1 and (st[d] * es) % 16:
             return False
     return True
 
@@ -96,31 +97,28 @@ def _seq(t):
 
 
 def _seq_desc(t):
-    s = [t.stride(d) if t.size(d) > 1 else 0 for d in range(3)]
-    return L.Seq(t.data_ptr(), s[0], s[1], s[2])
+    sh, st = t.shape, t.stride()
+    return L.Seq(t.data_ptr(), st[0] if sh[0] > 1 else 0, st[1] if sh[1] > 1 else 0, st[2] if sh[2] > 1 else 0)
 
 
-def _narrow_desc(t):
-    """[N,H,L,1] tensors (delta beta): any strides."""
-    s = [t.stride(d) if t.size(d) > 1 else 0 for d in range(3)]
-    return L.Seq(t.data_ptr(), s[0], s[1], s[2])
+_narrow_desc = _seq_desc      # [N,H,L,1] tensors (delta beta): any strides
 
 
 def _state_ok(t):
-    X = t.size(-1)
-    if t.dtype != torch.float32 or t.data_ptr() % 16:
+    if t.dtype is not torch.float32 or t.data_ptr() % 16:
         return False
-    if t.stride(-1) != 1 or t.stride(-2) != X:
+    sh, st = t.shape, t.stride()
+    if st[3] != 1 or st[2] != sh[3]:
         return False
     for d in range(2):
-        if t.size(d) > 1 and (t.stride(d) * 4) % 16:
+        if sh[d] > 1 and (st[d] * 4) % 16:
             return False
     return True
 
 
 def _state_desc(t):
-    s = [t.stride(d) if t.size(d) > 1 else 0 for d in range(2)]
-    return L.State(t.data_ptr(), s[0], s[1])
+    sh, st = t.shape, t.stride()
+    return L.State(t.data_ptr(), st[0] if sh[0] > 1 else 0, st[1] if sh[1] > 1 else 0)
 
 
 def _like(t, last=None):
@@ -193,14 +191,9 @@ def srwm_forward(x, W_y, W_q, W_k, w_b, save=True, variant=None):
     a.out = _seq_desc(out)
     saved = None
     if save:
-        f32 = dict(device=dev, dtype=torch.float32)
-        q = torch.empty((N, H, Ln, E), **f32)
-        k = torch.empty((N, H, Ln, E), **f32)
-        beta = torch.empty((N, H, Ln, 4), **f32)
-        yd = torch.empty((N, H, Ln, E), **f32)
-        qd = torch.empty((N, H, Ln, E), **f32)
-        kd = torch.empty((N, H, Ln, E), **f32)
-        bd = torch.empty((N, H, Ln, 4), **f32)
+        # two allocations for the seven saved tensors (they live and die together)
+        q, k, yd, qd, kd = torch.empty((5, N, H, Ln, E), device=dev, dtype=torch.float32).unbind(0)
+        beta, bd = torch.empty((2, N, H, Ln, 4), device=dev, dtype=torch.float32).unbind(0)
         saved = (q, k, beta, yd, qd, kd, bd)
         a.q, a.k, a.beta = _seq_desc(q), _seq_desc(k), _seq_desc(beta)
         a.y_diff, a.q_diff, a.k_diff, a.beta_diff = (_seq_desc(t) for t in (yd, qd, kd, bd))
