@@ -37,7 +37,7 @@ sys.path.insert(0, os.path.join(ROOT, "modern-srwm_b200"))
 
 import torch  # noqa: E402
 
-# ---- workloads (BASELINE.json configs; inputs are seeded synthetic tensors of those shapes) ----
+# ---- workloads (the benchmark configurations; inputs are seeded synthetic tensors of those shapes) ----
 WORKLOADS = {
     # name: op, B (global), H, L, E, dtype
     "srwm_c5": dict(op="srwm", B=1024, H=16, L=2048, E=64, dtype="bf16"),
@@ -58,7 +58,7 @@ CPU_SAMPLE = {"srwm": dict(B=4, L=256), "delta": dict(B=4, L=512)}
 
 def algorithmic_bytes(op, E, s, per="fwd+bwd"):
     """Bytes per (sequence, step) that the operator must move (s = bytes per activation
-    element), and bytes per sequence for the state; see DESIGN.md 'Roofline accounting'."""
+    element), and bytes per sequence for the state."""
     D = 3 * E + 4
     if op == "srwm":
         fwd = E * s + E * s + (5 * E + 8) * 4              # x read, y write, saved write

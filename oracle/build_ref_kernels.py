@@ -26,9 +26,14 @@ JOBS = [
 ]
 
 
+def built():
+    return all(os.path.exists(os.path.join(OUT, name, name + ".so")) for name, _, _ in JOBS)
+
+
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MODERN_SRWM_REFERENCE", os.path.join(HERE, "..", "..", "reference")),
+                    help="root of the upstream modern-srwm checkout")
     args = ap.parse_args()
     os.environ.setdefault("TORCH_CUDA_ARCH_LIST", "10.0a")
     from torch.utils.cpp_extension import load

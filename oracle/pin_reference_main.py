@@ -123,7 +123,8 @@ def _run_main(path, class_names):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("MODERN_SRWM_REFERENCE", os.path.join(HERE, "..", "..", "reference")),
+                    help="root of the upstream modern-srwm checkout")
     ap.add_argument("--out", default=os.path.join(HERE, "..", "tests", "golden"))
     args = ap.parse_args()
     os.makedirs(args.out, exist_ok=True)

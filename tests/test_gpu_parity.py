@@ -485,3 +485,42 @@ def test_layer_style_call_needs_no_layout_copies():
     assert orc.rel_max(hd.grad.cpu(), hr.grad) < GRAD_TOL
     for a, b in zip(sd, sr):
         assert orc.rel_max(a.grad.cpu(), b.grad) < GRAD_TOL
+
+
+def test_concurrent_calls_from_two_threads_and_streams():
+    # the RL code calls the operator from a learner and an inference thread at the same time
+    # (polybeast_learner.py:363,399): calls must be re-entrant and honour torch's current stream
+    import threading
+    sb = _sb()
+    d = _dev()
+    cases = []
+    for seed, (N, H, L, E) in enumerate([(3, 4, 60, 32), (2, 8, 45, 16)]):
+        x, Ws, go = srwm_inputs(N, H, L, E, seed=200 + seed)
+        f = orc.srwm_forward_explicit(x.double(), *[w.double() for w in Ws])
+        r = orc.srwm_backward_explicit(x.double(), f["q"], f["k"], f["beta"], f["y_diff"], f["q_diff"], f["k_diff"],
+                                       f["beta_diff"], go.double(), f["W_y"], f["W_q"], f["W_k"], f["w_b"])
+        cases.append((x.to(d), [w.to(d) for w in Ws], go.to(d), f, r))
+    errors = []
+
+    def worker(i):
+        try:
+            x, Ws, go, f, r = cases[i]
+            stream = torch.cuda.Stream(device=d)
+            with torch.cuda.stream(stream):
+                for _ in range(20):
+                    Wd = [w.clone() for w in Ws]
+                    out, saved = sb.srwm_forward(x, *Wd)
+                    grads = sb.srwm_backward(x, saved, go, *Wd)
+                stream.synchronize()
+            assert orc.rel_max(out.cpu(), f["out"]) < FWD_TOL
+            for t, o in zip(grads, r[:5]):
+                assert orc.rel_max(t.cpu(), o) < GRAD_TOL
+        except Exception as e:  # noqa: BLE001
+            errors.append((i, repr(e)))
+
+    threads = [threading.Thread(target=worker, args=(i,)) for i in range(2)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
