@@ -524,3 +524,10 @@ def test_concurrent_calls_from_two_threads_and_streams():
     for t in threads:
         t.join()
     assert not errors, errors
+
+
+@pytest.mark.parametrize("E", [8, 16, 32, 64])
+@pytest.mark.parametrize("strided", [False, True])
+def test_bf16_activations_every_head_size(E, strided):
+    _srwm_check(2, 3, 29, E, dtype=torch.bfloat16, strided=strided, state_grad=True)
+    _delta_check(2, 3, 29, E, dtype=torch.bfloat16, strided=strided)
