@@ -309,15 +309,19 @@ __device__ __forceinline__ float warp_max(float v) {
 
 template <typename TIO, int E, int T, bool PK, int MINB, bool DPRE, int NRP>
 __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdParams p) {
-  static_assert(E == 32 || E == 64, "column layout needs a whole warp of columns per block");
+  static_assert(E == 16 || E == 32 || E == 64, "column layout: one warp per block");
   // Lane (cq, rp) of a warp holds CPL adjacent columns x RL rows (row part rp of NRP) of the
   // warp's block.  NRP = 1 is the pure column layout; NRP > 1 trades a log2(NRP)-stage
   // shuffle per pass for 1/NRP of the broadcast operand loads (the shared-memory data pipe
   // is the busiest unit of this kernel).
   using SM = SrwmFwdColSmem<TIO, E, T>;
-  constexpr int P = 96, CPL = (E / 32) * NRP, RL = E / NRP, RL2 = RL / 2, VPL = CPL / NRP, RB = E / 8;
+  // At E = 16 a block has only 16 columns: NRP = 2 with one column per lane, and the two
+  // row-part lanes of a column both end up holding its (duplicated) pre-activation (DUP).
+  constexpr int P = 96, CPL = (E * NRP) / 32, RL = E / NRP, RL2 = RL / 2, RB = E / 8;
+  constexpr bool DUP = CPL < NRP;
+  constexpr int VPL = DUP ? CPL : CPL / NRP;
   static_assert(NRP == 1 || NRP == 2 || NRP == 4, "row parts per column group");
-  static_assert(RL % 4 == 0 && CPL % NRP == 0, "bad column-layout shape");
+  static_assert(CPL >= 1 && (CPL * 32) == E * NRP && RL % 4 == 0 && (DUP || CPL % NRP == 0), "bad column-layout shape");
   const int tid = threadIdx.x;
   const int warp = tid / 32, lane = tid % 32;
   const int rp = lane % NRP, c0 = (lane / NRP) * CPL;
@@ -343,11 +347,15 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
   u64 W[RL2][CPL];
   float* gW = (warp == 0 ? p.Wy : (warp == 1 ? p.Wq : p.Wk)).mat(n, h);
   float* gwb = p.wb.mat(n, h);
+  // local row r of row part rp is global row ((r/4)*NRP + rp)*4 + r%4: quads of rows are
+  // interleaved over the row parts, so the lanes of a warp read an operand vector as adjacent
+  // 16-byte pieces (no shared-memory bank conflict between row parts)
+  auto grow = [&](int r) { return ((r / 4) * NRP + rp) * 4 + (r % 4); };
 #pragma unroll
   for (int e2 = 0; e2 < RL2; ++e2) {
     float a[CPL], b[CPL];
-    ld_vec<CPL>(gW + (rp * RL + 2 * e2) * E + c0, a);
-    ld_vec<CPL>(gW + (rp * RL + 2 * e2 + 1) * E + c0, b);
+    ld_vec<CPL>(gW + grow(2 * e2) * E + c0, a);
+    ld_vec<CPL>(gW + grow(2 * e2 + 1) * E + c0, b);
 #pragma unroll
     for (int c = 0; c < CPL; ++c) W[e2][c] = pack2(a[c], b[c]);
   }
@@ -398,7 +406,7 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       for (int cc = 0; cc < CPL; ++cc) { a0[cc] = 0ull; a1[cc] = 0ull; }
 #pragma unroll
       for (int e4 = 0; e4 < RL / 4; ++e4) {
-        const float4 xv = reinterpret_cast<const float4*>(xr + rp * RL)[e4];
+        const float4 xv = reinterpret_cast<const float4*>(xr)[e4 * NRP + rp];
         const u64 p0 = pack2(xv.x, xv.y), p1 = pack2(xv.z, xv.w);
 #pragma unroll
         for (int cc = 0; cc < CPL; ++cc) {
@@ -409,13 +417,21 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       float v[CPL];
 #pragma unroll
       for (int cc = 0; cc < CPL; ++cc) v[cc] = hsum2(a0[cc]) + hsum2(a1[cc]);
-      reduce_scatter<CPL, NRP, 1>(v, lane);   // lane rp keeps columns c0 + rp*VPL .. + VPL
       float vs[VPL];
+      int cs;
+      if constexpr (DUP) {
 #pragma unroll
-      for (int i = 0; i < VPL; ++i) vs[i] = v[i];
-      const int cs = c0 + rp * VPL;
+        for (int i = 0; i < CPL; ++i) vs[i] = allreduce_rows<NRP>(v[i]);   // every row-part lane gets the column
+        cs = c0;
+      } else {
+        reduce_scatter<CPL, NRP, 1>(v, lane);   // lane rp keeps columns c0 + rp*VPL .. + VPL
+#pragma unroll
+        for (int i = 0; i < VPL; ++i) vs[i] = v[i];
+        cs = c0 + rp * VPL;
+      }
+      const bool writer = !DUP || rp == 0;
       if (warp == 0) {
-        st_vec<VPL>(sy + t * E + cs, vs);
+        if (writer) st_vec<VPL>(sy + t * E + cs, vs);
         float xrow[RB], wrow[RB];
         ld_vec<RB>(xr + r8 * RB, xrow);
         ld_vec<RB>(wbT + jb * E + r8 * RB, wrow);
@@ -433,15 +449,15 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
 #pragma unroll
         for (int i = 0; i < VPL; ++i) { vs[i] = __expf(vs[i] - m); ssum += vs[i]; }
         ssum = allreduce_warp(ssum);
-        const float inv = __fdividef(1.f, ssum);
+        const float inv = __fdividef(DUP ? (float)NRP : 1.f, ssum);   // duplicated columns were summed NRP times
 #pragma unroll
         for (int i = 0; i < VPL; ++i) vs[i] *= inv;
-        st_vec<VPL>((warp == 1 ? sq : sk) + t * E + cs, vs);
+        if (writer) st_vec<VPL>((warp == 1 ? sq : sk) + t * E + cs, vs);
         if constexpr (DPRE) {
           // the k warp publishes q - k once for everybody: it needs q from the q warp,
           // handed over through a two-warp named barrier
           asm volatile("bar.sync 1, 64;" ::: "memory");
-          if (warp == 2) {
+          if (warp == 2 && writer) {
             float qv[VPL];
             ld_vec<VPL>(qr + cs, qv);
 #pragma unroll
@@ -459,12 +475,12 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       for (int e4 = 0; e4 < RL / 4; ++e4) {
         u64 d0, d1;
         if constexpr (DPRE) {
-          const float4 dv = reinterpret_cast<const float4*>(dq + rp * RL)[e4];
+          const float4 dv = reinterpret_cast<const float4*>(dq)[e4 * NRP + rp];
           d0 = pack2(dv.x, dv.y);
           d1 = pack2(dv.z, dv.w);
         } else {
-          const float4 qv = reinterpret_cast<const float4*>(qr + rp * RL)[e4];
-          const float4 kv = reinterpret_cast<const float4*>(kr + rp * RL)[e4];
+          const float4 qv = reinterpret_cast<const float4*>(qr)[e4 * NRP + rp];
+          const float4 kv = reinterpret_cast<const float4*>(kr)[e4 * NRP + rp];
           d0 = fma2<PK>(pack2(kv.x, kv.y), neg1, pack2(qv.x, qv.y));
           d1 = fma2<PK>(pack2(kv.z, kv.w), neg1, pack2(qv.z, qv.w));
         }
@@ -500,7 +516,7 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       // ---- rank-1 update -------------------------------------------------------------------
 #pragma unroll
       for (int e4 = 0; e4 < RL / 4; ++e4) {
-        const float4 kv = reinterpret_cast<const float4*>(kr + rp * RL)[e4];
+        const float4 kv = reinterpret_cast<const float4*>(kr)[e4 * NRP + rp];
         const u64 k0 = pack2(kv.x, kv.y), k1 = pack2(kv.z, kv.w);
 #pragma unroll
         for (int cc = 0; cc < CPL; ++cc) {
@@ -528,8 +544,8 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
     float a[CPL], b[CPL];
 #pragma unroll
     for (int cc = 0; cc < CPL; ++cc) unpack2(W[e2][cc], a[cc], b[cc]);
-    st_vec<CPL>(gW + (rp * RL + 2 * e2) * E + c0, a);
-    st_vec<CPL>(gW + (rp * RL + 2 * e2 + 1) * E + c0, b);
+    st_vec<CPL>(gW + grow(2 * e2) * E + c0, a);
+    st_vec<CPL>(gW + grow(2 * e2 + 1) * E + c0, b);
   }
   __syncthreads();
   for (int i = tid; i < 4 * E; i += P) gwb[i] = wbT[(i % 4) * E + i / 4];
