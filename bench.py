@@ -515,7 +515,7 @@ def run_ours(args):
 # divided by sequences x steps; profiles/*_d64_bf16_*.txt).  `roofline.traffic` scales this
 # to a full launch by the sequence-steps it processes (traffic is streamed once, so it
 # grows in proportion).
-NCU_BWD_DRAM_BYTES_PER_SEQ_STEP = {"srwm": 1842.0, "delta": 1423.7}
+NCU_BWD_DRAM_BYTES_PER_SEQ_STEP = {"srwm": 1841.0, "delta": 1423.7}
 
 
 def run_table(args):
