@@ -834,33 +834,39 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       __syncthreads();
 
       // ================= phase 2 =================
-      float gqc[C], gkc[C], sc[8];
+      // The 2C values gq~ / gk~ of this column group are needed by all its NRG lanes.  Each lane
+      // finishes a share of them (sum of the per-warp partials, softmax backward) and the
+      // lanes exchange the results with shuffles, instead of every lane redoing all of them.
+      constexpr int VPLN = (2 * C + NRG - 1) / NRG;   // values finished per lane
+      float mine[VPLN];
 #pragma unroll
-      for (int j = 0; j < C; ++j) { gqc[j] = 0.f; gkc[j] = 0.f; }
+      for (int u = 0; u < VPLN; ++u) {
+        const int v = rg + u * NRG;                   // 0..C-1: gq~ of column v ; C..2C-1: gk~ of column v-C
+        const int which = (v >= C) ? 1 : 0;
+        const int col = cg * C + (which ? v - C : v);
+        float acc = 0.f, dot = 0.f;
+        if (v < 2 * C) {
 #pragma unroll
-      for (int i = 0; i < 8; ++i) sc[i] = 0.f;
-#pragma unroll
-      for (int w = 0; w < NWARP; ++w) {
-        float a[C], b[C], s8[8];
-        ld_vec<C>(xrow + (par * NWARP + w) * 2 * E + cg * C, a);
-        ld_vec<C>(xrow + (par * NWARP + w) * 2 * E + E + cg * C, b);
-        ld_vec<8>(xsc + (par * NWARP + w) * 8, s8);
-#pragma unroll
-        for (int j = 0; j < C; ++j) { gqc[j] += a[j]; gkc[j] += b[j]; }
-#pragma unroll
-        for (int i = 0; i < 6; ++i) sc[i] += s8[i];
+          for (int w = 0; w < NWARP; ++w) {
+            acc += xrow[(par * NWARP + w) * 2 * E + which * E + col];
+            dot += xsc[(par * NWARP + w) * 8 + 4 + which];
+          }
+          const float sm_val = (which ? sk : sq)[t * E + col];
+          acc = sm_val * (acc - dot);
+        }
+        mine[u] = acc;
       }
       float pre[3][C];
-      {
-        float qc[C], kc[C];
-        ld_vec<C>(sq + t * E + cg * C, qc);
-        ld_vec<C>(sk + t * E + cg * C, kc);
-        ld_vec<C>(sg + t * E + cg * C, pre[0]);
+      ld_vec<C>(sg + t * E + cg * C, pre[0]);
 #pragma unroll
-        for (int j = 0; j < C; ++j) {
-          pre[1][j] = qc[j] * (gqc[j] - sc[4]);
-          pre[2][j] = kc[j] * (gkc[j] - sc[5]);
-        }
+      for (int j = 0; j < C; ++j) {
+        pre[1][j] = __shfl_sync(0xffffffffu, mine[j / NRG], (lane & ~(NRG - 1)) + (j % NRG));
+        pre[2][j] = __shfl_sync(0xffffffffu, mine[(C + j) / NRG], (lane & ~(NRG - 1)) + ((C + j) % NRG));
+      }
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (jb >= 0) {
+#pragma unroll
+        for (int w = 0; w < NWARP; ++w) sc[0] += xsc[(par * NWARP + w) * 8 + jb];
       }
       float xr[R];
       ld_rows<R, NRG>(sx + t * E, rg, xr);
@@ -892,7 +898,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         ld_rows<R, NRG>(wbT + jb * E, rg, wr);
         ld_rows<R, NRG>(gbT + jb * E, rg, gr);
         const float b = sbeta[t * 4 + jb];
-        const float pb = sc[jb] * b * (1.f - b);
+        const float pb = sc[0] * b * (1.f - b);
 #pragma unroll
         for (int i = 0; i < R; ++i) {
           gxr[i] = fmaf(wr[i], pb, gxr[i]);
