@@ -49,7 +49,7 @@ extern "C" {
 #define SRWM_B200_ERR_ALIGN      -5  /* a row does not start on a 16-byte boundary        */
 #define SRWM_B200_ERR_VARIANT    -6  /* tuning variant id not compiled in                 */
 #define SRWM_B200_ERR_CUDA       -7  /* CUDA runtime error; see srwm_b200_last_cuda_error */
-#define SRWM_B200_ERR_TOO_LARGE  -8  /* size beyond a fixed capacity (no-alloc entry)     */
+#define SRWM_B200_ERR_TOO_LARGE  -8  /* size beyond a fixed capacity (reserved)           */
 
 /* flags */
 #define SRWM_B200_FLAG_NO_SAVE        1u /* forward: do not write the saved-for-backward

@@ -64,7 +64,7 @@ def build(force=False, verbose=False):
             obj = os.path.join(OBJ, f"{tu}_{'bf16' if bf else 'f32'}.o")
             if force or _stale(obj, [src] + hdrs):
                 jobs.append((src, obj, [f"-DSRWM_TIO_BF16={bf}"], verbose))
-    for name in ("api", "noalloc"):
+    for name in ("api",):
         src = os.path.join(CSRC, name + ".cu")
         if not os.path.exists(src):
             continue

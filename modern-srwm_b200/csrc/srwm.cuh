@@ -588,6 +588,14 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
   constexpr int S_ROW = SCATTER ? (2 * R) / CGW : R;   // [u | gk] values per lane after the scatter
   constexpr int S_GX = SCATTER ? R / CGW : R;
   constexpr int S_SC = SCATTER ? 8 / NRG : 8;
+  // column sums (3C+1 values over the NRG row-group lanes): padded to a power of two
+  constexpr int NVC = 3 * C + 1;
+  constexpr int PADN = NVC <= 4 ? 4 : (NVC <= 8 ? 8 : 16);
+  constexpr int S_COL = PADN / NRG > 0 ? PADN / NRG : 1;
+  // (at E = 64 the state already fills the register file and the scatter's staging array spills:
+  // measured slower there, faster at E <= 32)
+  constexpr bool RSCAT = (E <= 32) && (NRG >= 2) && (PADN % NRG == 0) && (PADN >= NRG) && (C % S_COL == 0) &&
+                         (NVC <= 16);
   const int tid = threadIdx.x;
   const int rg = tid % NRG, cg = tid / NRG;
   const int warp = tid / 32, lane = tid % 32;
@@ -729,21 +737,58 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       }
       // complete r over the row groups; gd = b r; scalar partials r.d
       float sc8[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      float gdb;
+      if constexpr (RSCAT) {
+        // reduce-scatter the 3C+1 column sums over the row-group lanes, let each lane finish its
+        // S of them (all of one block, since S divides C), then hand every lane all of gd
+        float v[PADN];
 #pragma unroll
-      for (int z = 0; z < 3; ++z) {
-        float dz[C];
-        ld_vec<C>((z == 0 ? syd : (z == 1 ? sqd : skd)) + t * E + cg * C, dz);
+        for (int i = 0; i < PADN; ++i) v[i] = 0.f;
 #pragma unroll
-        for (int j = 0; j < C; ++j) {
-          const float r = allreduce_rows<NRG>(rcol[z][j]);
-          sc8[z] = fmaf(r, dz[j], sc8[z]);
-          rcol[z][j] = beta[z] * r;   // now gd
+        for (int z = 0; z < 3; ++z)
+#pragma unroll
+          for (int j = 0; j < C; ++j) v[z * C + j] = rcol[z][j];
+        v[3 * C] = rb;
+        reduce_scatter<PADN, NRG, 1>(v, lane);
+        const int g0 = rg * S_COL;
+        const int zl = min(g0 / C, 3);                     // block of this lane's values (3: the w_b column)
+        const float bz = sbeta[t * 4 + zl];
+        float fin[S_COL], sbl = 0.f;
+#pragma unroll
+        for (int i = 0; i < S_COL; ++i) {
+          const int g = g0 + i;
+          float dzv;
+          if (zl < 3) dzv = syd[zl * T * E + t * E + cg * C + (g % C)];   // y_diff, q_diff, k_diff rows are adjacent
+          else dzv = (g == 3 * C && jb >= 0) ? sbd[t * 4 + jb] : 0.f;
+          sbl = fmaf(v[i], dzv, sbl);
+          fin[i] = bz * v[i];
         }
+#pragma unroll
+        for (int zz = 0; zz < 4; ++zz) sc8[zz] = (zl == zz) ? sbl : 0.f;
+        const int base = lane & ~(NRG - 1);
+#pragma unroll
+        for (int z = 0; z < 3; ++z)
+#pragma unroll
+          for (int j = 0; j < C; ++j)
+            rcol[z][j] = __shfl_sync(0xffffffffu, fin[(z * C + j) % S_COL], base + (z * C + j) / S_COL);   // now gd
+        gdb = __shfl_sync(0xffffffffu, fin[(3 * C) % S_COL], base + (3 * C) / S_COL);
+      } else {
+#pragma unroll
+        for (int z = 0; z < 3; ++z) {
+          float dz[C];
+          ld_vec<C>((z == 0 ? syd : (z == 1 ? sqd : skd)) + t * E + cg * C, dz);
+#pragma unroll
+          for (int j = 0; j < C; ++j) {
+            const float r = allreduce_rows<NRG>(rcol[z][j]);
+            sc8[z] = fmaf(r, dz[j], sc8[z]);
+            rcol[z][j] = beta[z] * r;   // now gd
+          }
+        }
+        rb = allreduce_rows<NRG>(rb);
+        gdb = beta[3] * rb;
+        sc8[3] = rb * bdj;
+        if (rg != 0) { sc8[0] = 0.f; sc8[1] = 0.f; sc8[2] = 0.f; sc8[3] = 0.f; }   // count each column once
       }
-      rb = allreduce_rows<NRG>(rb);
-      const float gdb = beta[3] * rb;
-      sc8[3] = rb * bdj;
-      if (rg != 0) { sc8[0] = 0.f; sc8[1] = 0.f; sc8[2] = 0.f; sc8[3] = 0.f; }   // count each column once
       // G += (q-k)^T gd ; u = W(t-1) gd (row partial)
       u64 d2[R2], u2[R2];
       {
