@@ -34,7 +34,7 @@
 extern "C" {
 #endif
 
-#define SRWM_B200_ABI_VERSION 1
+#define SRWM_B200_ABI_VERSION 2
 
 /* io_dtype */
 #define SRWM_B200_F32  0
@@ -59,6 +59,11 @@ extern "C" {
                                             without it they are treated as zero on entry     */
 #define SRWM_B200_FLAG_RESTORE_STATE  4u /* SRWM backward: also write the rebuilt initial
                                             state W_0 back into W_* (the reference leaves W_L) */
+#define SRWM_B200_FLAG_INPUT_SOFTMAX  8u /* SRWM forward/backward: x holds RAW activations and the
+                                            kernels apply softmax over the head dimension (the
+                                            callers' F.softmax, supervised_learning/layer.py:162-163,
+                                            reinforcement_learning/torchbeast/layer.py:383);
+                                            grad_x is then the gradient of the raw values      */
 
 typedef struct srwm_b200_seq {      /* [N,H,L,X] view, innermost contiguous */
   void*   data;
@@ -130,6 +135,72 @@ typedef struct srwm_b200_srwm_bwd_args {
 int srwm_b200_srwm_backward(const srwm_b200_srwm_bwd_args* args, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------
+ * Layer-level SRWM calls: what the callers do around the kernel, taken into it.  No
+ * reference function corresponds one to one; each piece cites the caller code it absorbs.
+ *
+ * With an extension block whose base_* are set, the state is  W = base + shift:
+ *   - base_*   the un-repeated slow weights [1,H,E,.] (stride_n = 0) -- the callers'
+ *              `self.W_y.repeat(bsz,1,1,1)` (supervised_learning/layer.py:169-177,
+ *              reinforcement_learning/torchbeast/layer.py:392-395) is never materialised;
+ *   - shift_*  optional initial shift [N,H,E,.] (the carried `state`; NULL data = zero);
+ *   - forward: W_y, W_q, W_k, w_b of the main block are OUTPUTS only and receive the final
+ *              shift  W_L - base  (the callers' subtraction, layer.py:200-204 / :412-415);
+ *   - backward: W_* hold that final shift on entry (W_L = base + W_*); with RESTORE_STATE they
+ *              receive W_0 - base.  grad_W_* are dL/dW_0 per sample, as in the plain call:
+ *              dL/dshift = grad_W_*, dL/dbase = their sum over the batch
+ *              (srwm_b200_reduce_batch) minus the sum of the incoming dL/dshift_out;
+ *   - done     optional bytes [N,L] (forward): done[n,t] != 0 sets the shift of sample n to
+ *              zero before step t -- the per-step `nd * state` of the learner's unroll
+ *              (reinforcement_learning/torchbeast_procgen/model.py:1180-1194), which lets T
+ *              one-step calls become one call of length T.  The reverse-time backward cannot
+ *              cross such a reset (the pre-reset state is gone); use the detached backward.
+ * ext == NULL (or all base_* NULL) makes these identical to the plain calls above.
+ * ---------------------------------------------------------------------------------- */
+typedef struct srwm_b200_srwm_ext {
+  srwm_b200_state base_W_y, base_W_q, base_W_k;    /* [1 or N, H, E, E] */
+  srwm_b200_state base_w_b;                        /* [1 or N, H, E, 4] */
+  srwm_b200_state shift_W_y, shift_W_q, shift_W_k, shift_w_b;   /* optional, forward only */
+  const uint8_t*  done;                            /* optional, forward only */
+  int64_t done_stride_n, done_stride_l;            /* bytes */
+} srwm_b200_srwm_ext;
+
+int srwm_b200_srwm_layer_forward(const srwm_b200_srwm_fwd_args* args, const srwm_b200_srwm_ext* ext,
+                                 void* cuda_stream);
+int srwm_b200_srwm_layer_backward(const srwm_b200_srwm_bwd_args* args, const srwm_b200_srwm_ext* ext,
+                                  void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------
+ * SRWM backward with the state DETACHED at every step: the gradient the reference's
+ * reinforcement-learning learner computes, which calls the layer one step at a time and
+ * detaches the state it carries (reinforcement_learning/torchbeast/layer.py:412-421 under
+ * torchbeast_procgen/model.py:1180-1197).  Only out_t = x_t.W_y(t-1) carries gradient:
+ *   grad_x_t = W_y(t-1) grad_out_t  (through the input softmax with INPUT_SOFTMAX),
+ *   grad_W_y = sum_t x_t^T grad_out_t  per sample;   W_q, W_k, w_b receive none.
+ * W_y(t-1) is replayed forward in time from base_W_y (+ shift_W_y) with the saved k, beta,
+ * y_diff of the forward, returning to base where done is set.
+ * ---------------------------------------------------------------------------------- */
+typedef struct srwm_b200_srwm_bwd_detached_args {
+  int32_t N, H, L, E;
+  int32_t io_dtype;
+  uint32_t flags;                   /* INPUT_SOFTMAX */
+  int32_t variant;
+  int32_t reserved;
+  srwm_b200_seq   x;                /* in  [N,H,L,E] io_dtype */
+  srwm_b200_seq   k;                /* in  saved fp32 */
+  srwm_b200_seq   beta;             /* in  saved fp32 [N,H,L,4] */
+  srwm_b200_seq   y_diff;           /* in  saved fp32 */
+  srwm_b200_seq   grad_out;         /* in  [N,H,L,E] io_dtype */
+  srwm_b200_state base_W_y;         /* in  W_y before the first step, or the slow weights */
+  srwm_b200_state shift_W_y;        /* in  optional initial shift (NULL data = none) */
+  const uint8_t*  done;             /* in  optional [N,L] */
+  int64_t done_stride_n, done_stride_l;
+  srwm_b200_seq   grad_x;           /* out [N,H,L,E] io_dtype */
+  srwm_b200_state grad_W_y;         /* out [N,H,E,E] fp32 */
+} srwm_b200_srwm_bwd_detached_args;
+
+int srwm_b200_srwm_backward_detached(const srwm_b200_srwm_bwd_detached_args* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------
  * Delta-rule forward.  Replaces
  *   void fast_weight_forward(Q, K, V, beta, v_old, v_insert, kv, out)
  *   supervised_learning/fast_weight/fast_weight_cuda.cu:182-240 (kernel :17-178), bound at
@@ -194,7 +265,8 @@ int srwm_b200_reduce_batch(const float* src, int64_t stride_n, int32_t N, int64_
 int         srwm_b200_abi_version(void);
 int         srwm_b200_head_dim_supported(int32_t E);           /* 1 / 0 */
 int         srwm_b200_num_variants(int32_t op, int32_t E);     /* op: 0 srwm_fwd 1 srwm_bwd
-                                                                  2 delta_fwd 3 delta_bwd */
+                                                                  2 delta_fwd 3 delta_bwd
+                                                                  4 srwm_bwd_detached */
 const char* srwm_b200_strerror(int code);
 int         srwm_b200_last_cuda_error(void);   /* cudaError_t of the last failed call of the
                                                   calling thread, 0 if none */

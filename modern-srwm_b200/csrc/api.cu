@@ -46,6 +46,32 @@ inline int check_dims(int N, int H, int L, long long* grid) {
   return 0;
 }
 
+// Extension block of the layer-level calls: all four base_* or none; shift and done need a
+// base.  Sets the kernels' flag bits.
+inline int check_ext(const srwm_b200_srwm_ext* x, bool forward, unsigned* flags) {
+  *flags = 0;
+  if (!x) return 0;
+  const int nb = (x->base_W_y.data != nullptr) + (x->base_W_q.data != nullptr) + (x->base_W_k.data != nullptr) +
+                 (x->base_w_b.data != nullptr);
+  const int ns = (x->shift_W_y.data != nullptr) + (x->shift_W_q.data != nullptr) + (x->shift_W_k.data != nullptr) +
+                 (x->shift_w_b.data != nullptr);
+  if (nb != 0 && nb != 4) return SRWM_B200_ERR_NULL;
+  if (ns != 0 && ns != 4) return SRWM_B200_ERR_NULL;
+  if (nb == 0) return (ns != 0 || x->done != nullptr) ? SRWM_B200_ERR_NULL : 0;
+  if (!state_aligned(x->base_W_y) || !state_aligned(x->base_W_q) || !state_aligned(x->base_W_k) ||
+      !state_aligned(x->base_w_b))
+    return SRWM_B200_ERR_ALIGN;
+  *flags |= srwm::F_BASE;
+  if (forward && ns == 4) {
+    if (!state_aligned(x->shift_W_y) || !state_aligned(x->shift_W_q) || !state_aligned(x->shift_W_k) ||
+        !state_aligned(x->shift_w_b))
+      return SRWM_B200_ERR_ALIGN;
+    *flags |= srwm::F_SHIFT_IN;
+  }
+  if (forward && x->done) *flags |= srwm::F_DONE;
+  return 0;
+}
+
 inline int finish(int rc, int cuda_err) {
   if (rc == -7) {
     g_last_cuda_error = cuda_err;
@@ -100,6 +126,12 @@ int srwm_b200_describe(int32_t op, int32_t E, int32_t io_dtype, int32_t variant,
               : srwm::dispatch_srwm_bwd_f32(E, variant, p, 0, 0, &info, 1, &ce);
       break;
     }
+    case srwm::OP_SRWM_BWD_DET: {
+      srwm::SrwmBwdDetParams p = {};
+      rc = bf ? srwm::dispatch_srwm_bwd_det_bf16(E, variant, p, 0, 0, &info, 1, &ce)
+              : srwm::dispatch_srwm_bwd_det_f32(E, variant, p, 0, 0, &info, 1, &ce);
+      break;
+    }
     case srwm::OP_DELTA_FWD: {
       srwm::DeltaFwdParams p = {};
       rc = bf ? srwm::dispatch_delta_fwd_bf16(E, variant, p, 0, 0, &info, 1, &ce)
@@ -129,6 +161,14 @@ int srwm_b200_num_variants(int32_t op, int32_t E) {
 
 // ---------------------------------------------------------------------------------------
 int srwm_b200_srwm_forward(const srwm_b200_srwm_fwd_args* a, void* stream) {
+  return srwm_b200_srwm_layer_forward(a, nullptr, stream);
+}
+
+int srwm_b200_srwm_backward(const srwm_b200_srwm_bwd_args* a, void* stream) {
+  return srwm_b200_srwm_layer_backward(a, nullptr, stream);
+}
+
+int srwm_b200_srwm_layer_forward(const srwm_b200_srwm_fwd_args* a, const srwm_b200_srwm_ext* x, void* stream) {
   if (!a) return SRWM_B200_ERR_NULL;
   long long grid;
   if (int rc = check_dims(a->N, a->H, a->L, &grid)) return rc;
@@ -148,9 +188,17 @@ int srwm_b200_srwm_forward(const srwm_b200_srwm_fwd_args* a, void* stream) {
     ok = ok && seq_aligned(a->q, 4) && seq_aligned(a->k, 4) && seq_aligned(a->beta, 4) && seq_aligned(a->y_diff, 4) &&
          seq_aligned(a->q_diff, 4) && seq_aligned(a->k_diff, 4) && seq_aligned(a->beta_diff, 4);
   if (!ok) return SRWM_B200_ERR_ALIGN;
+  unsigned ext_flags = 0;
+  if (int rc = check_ext(x, /*forward=*/true, &ext_flags)) return rc;
 
-  srwm::SrwmFwdParams p;
-  p.N = a->N; p.H = a->H; p.L = a->L; p.flags = a->flags;
+  srwm::SrwmFwdParams p = {};
+  p.N = a->N; p.H = a->H; p.L = a->L;
+  p.flags = (a->flags & (SRWM_B200_FLAG_NO_SAVE | SRWM_B200_FLAG_INPUT_SOFTMAX)) | ext_flags;
+  if (ext_flags & srwm::F_BASE) {
+    p.bWy = view(x->base_W_y); p.bWq = view(x->base_W_q); p.bWk = view(x->base_W_k); p.bwb = view(x->base_w_b);
+    p.sWy = view(x->shift_W_y); p.sWq = view(x->shift_W_q); p.sWk = view(x->shift_W_k); p.swb = view(x->shift_w_b);
+    p.done = x->done; p.done_sn = x->done_stride_n; p.done_sl = x->done_stride_l;
+  }
   p.x = view(a->x, es); p.out = view(a->out, es);
   p.q = view(a->q, 4); p.k = view(a->k, 4); p.beta = view(a->beta, 4);
   p.yd = view(a->y_diff, 4); p.qd = view(a->q_diff, 4); p.kd = view(a->k_diff, 4); p.bd = view(a->beta_diff, 4);
@@ -162,7 +210,7 @@ int srwm_b200_srwm_forward(const srwm_b200_srwm_fwd_args* a, void* stream) {
   return finish(rc, ce);
 }
 
-int srwm_b200_srwm_backward(const srwm_b200_srwm_bwd_args* a, void* stream) {
+int srwm_b200_srwm_layer_backward(const srwm_b200_srwm_bwd_args* a, const srwm_b200_srwm_ext* x, void* stream) {
   if (!a) return SRWM_B200_ERR_NULL;
   long long grid;
   if (int rc = check_dims(a->N, a->H, a->L, &grid)) return rc;
@@ -184,9 +232,16 @@ int srwm_b200_srwm_backward(const srwm_b200_srwm_bwd_args* a, void* stream) {
          seq_aligned(a->q, 4) && seq_aligned(a->k, 4) && seq_aligned(a->beta, 4) && seq_aligned(a->y_diff, 4) &&
          seq_aligned(a->q_diff, 4) && seq_aligned(a->k_diff, 4) && seq_aligned(a->beta_diff, 4);
   if (!ok) return SRWM_B200_ERR_ALIGN;
+  unsigned ext_flags = 0;
+  if (int rc = check_ext(x, /*forward=*/false, &ext_flags)) return rc;
 
-  srwm::SrwmBwdParams p;
-  p.N = a->N; p.H = a->H; p.L = a->L; p.flags = a->flags;
+  srwm::SrwmBwdParams p = {};
+  p.N = a->N; p.H = a->H; p.L = a->L;
+  p.flags = (a->flags & (SRWM_B200_FLAG_STATE_GRAD_IN | SRWM_B200_FLAG_RESTORE_STATE | SRWM_B200_FLAG_INPUT_SOFTMAX)) |
+            ext_flags;
+  if (ext_flags & srwm::F_BASE) {
+    p.bWy = view(x->base_W_y); p.bWq = view(x->base_W_q); p.bWk = view(x->base_W_k); p.bwb = view(x->base_w_b);
+  }
   p.x = view(a->x, es); p.gout = view(a->grad_out, es); p.gx = view(a->grad_x, es);
   p.q = view(a->q, 4); p.k = view(a->k, 4); p.beta = view(a->beta, 4);
   p.yd = view(a->y_diff, 4); p.qd = view(a->q_diff, 4); p.kd = view(a->k_diff, 4); p.bd = view(a->beta_diff, 4);
@@ -196,6 +251,39 @@ int srwm_b200_srwm_backward(const srwm_b200_srwm_bwd_args* a, void* stream) {
   const int rc = a->io_dtype == SRWM_B200_BF16
                      ? srwm::dispatch_srwm_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
                      : srwm::dispatch_srwm_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+  return finish(rc, ce);
+}
+
+int srwm_b200_srwm_backward_detached(const srwm_b200_srwm_bwd_detached_args* a, void* stream) {
+  if (!a) return SRWM_B200_ERR_NULL;
+  long long grid;
+  if (int rc = check_dims(a->N, a->H, a->L, &grid)) return rc;
+  if (!head_dim_ok(a->E)) return SRWM_B200_ERR_HEAD_DIM;
+  if (a->io_dtype != SRWM_B200_F32 && a->io_dtype != SRWM_B200_BF16) return SRWM_B200_ERR_DTYPE;
+  if (grid == 0) return 0;
+  if (!a->base_W_y.data || !a->grad_W_y.data) return SRWM_B200_ERR_NULL;
+  if (a->L > 0 && (!a->x.data || !a->k.data || !a->beta.data || !a->y_diff.data || !a->grad_out.data || !a->grad_x.data))
+    return SRWM_B200_ERR_NULL;
+  const int es = esize(a->io_dtype);
+  bool ok = state_aligned(a->base_W_y) && state_aligned(a->grad_W_y) &&
+            (a->shift_W_y.data == nullptr || state_aligned(a->shift_W_y));
+  if (a->L > 0)
+    ok = ok && seq_aligned(a->x, es) && seq_aligned(a->grad_out, es) && seq_aligned(a->grad_x, es) &&
+         seq_aligned(a->k, 4) && seq_aligned(a->beta, 4) && seq_aligned(a->y_diff, 4);
+  if (!ok) return SRWM_B200_ERR_ALIGN;
+
+  srwm::SrwmBwdDetParams p = {};
+  p.N = a->N; p.H = a->H; p.L = a->L;
+  p.flags = (a->flags & SRWM_B200_FLAG_INPUT_SOFTMAX) | (a->shift_W_y.data ? srwm::F_SHIFT_IN : 0u) |
+            (a->done ? srwm::F_DONE : 0u);
+  p.x = view(a->x, es); p.gout = view(a->grad_out, es); p.gx = view(a->grad_x, es);
+  p.k = view(a->k, 4); p.beta = view(a->beta, 4); p.yd = view(a->y_diff, 4);
+  p.bWy = view(a->base_W_y); p.sWy = view(a->shift_W_y); p.gWy = view(a->grad_W_y);
+  p.done = a->done; p.done_sn = a->done_stride_n; p.done_sl = a->done_stride_l;
+  int ce = 0;
+  const int rc = a->io_dtype == SRWM_B200_BF16
+                     ? srwm::dispatch_srwm_bwd_det_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
+                     : srwm::dispatch_srwm_bwd_det_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
   return finish(rc, ce);
 }
 

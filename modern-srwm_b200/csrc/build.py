@@ -25,7 +25,8 @@ LIB = os.path.join(PKG, "srwm_b200", "libsrwm_b200.so")
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 COMMON = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-I", INCLUDE, "-I", CSRC]
-KERNEL_TUS = ["kernels_srwm_fwd", "kernels_srwm_bwd", "kernels_delta_fwd", "kernels_delta_bwd"]
+KERNEL_TUS = ["kernels_srwm_fwd", "kernels_srwm_bwd", "kernels_srwm_bwd_det", "kernels_delta_fwd",
+              "kernels_delta_bwd"]
 
 
 def _nvcc():

@@ -331,4 +331,86 @@ struct StateView {
   __device__ __forceinline__ float* mat(int n, int h) const { return base + (long long)n * sn + (long long)h * sh; }
 };
 
+// Flag bits of the kernels' `flags` word (the first three are the ABI's; the rest are set by
+// the C layer from the extension block of a call).
+constexpr unsigned F_NO_SAVE = 1u, F_STATE_GRAD_IN = 2u, F_RESTORE = 4u, F_INPUT_SOFTMAX = 8u, F_BASE = 16u,
+                   F_SHIFT_IN = 32u, F_DONE = 64u;
+
+__device__ __forceinline__ float warp_max(float v) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
+  return r;
+}
+
+// Streamed rows to fp32 rows in shared memory (nt rows of E values).
+template <typename TIO, int E, int P>
+__device__ __forceinline__ void convert_rows(const TIO* src, float* dst, int nt, int tid) {
+  for (int i = tid; i < nt * E / 2; i += P) {
+    float v[2];
+    ld_vec<2>(src + 2 * i, v);
+    st_vec<2>(dst + 2 * i, v);
+  }
+}
+
+// Row-wise softmax of nt staged rows: dst[t][:] = softmax(src[t][:]) in fp32, one warp per row.
+// dst may be the same memory as src when the streamed type is float (a lane rewrites exactly
+// what it read).
+template <typename TIO, int E, int P>
+__device__ __forceinline__ void softmax_rows(const TIO* src, float* dst, int nt, int tid) {
+  constexpr int VPT = E >= 32 ? E / 32 : 1;
+  const int warp = tid / 32, lane = tid % 32;
+  const bool active = lane * VPT < E;
+  for (int t = warp; t < nt; t += P / 32) {
+    float v[VPT];
+    if (active) {
+      ld_vec<VPT>(src + t * E + lane * VPT, v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < VPT; ++i) v[i] = -INFINITY;
+    }
+    float m = v[0];
+#pragma unroll
+    for (int i = 1; i < VPT; ++i) m = fmaxf(m, v[i]);
+    m = warp_max(m);
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      v[i] = __expf(v[i] - m);
+      s += v[i];
+    }
+    s = allreduce_warp(s);
+    const float inv = __fdividef(1.f, s);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) v[i] *= inv;
+    if (active) st_vec<VPT>(dst + t * E + lane * VPT, v);
+  }
+}
+
+// Backward of that softmax, applied to finished gradient rows on their way out:
+// out[t][e] = x[t][e] (g[t][e] - sum_e' g[t][e'] x[t][e']), rows of g `gstride` floats apart,
+// written as streamed type to global rows `row_stride_bytes` apart.
+template <typename TIO, int E, int P>
+__device__ __forceinline__ void softmax_bwd_rows(const float* xs, const float* g, int gstride, char* grow0,
+                                                 long long row_stride_bytes, int nt, int tid) {
+  constexpr int VPT = E >= 32 ? E / 32 : 1;
+  const int warp = tid / 32, lane = tid % 32;
+  const bool active = lane * VPT < E;
+  for (int t = warp; t < nt; t += P / 32) {
+    float xv[VPT], gv[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) { xv[i] = 0.f; gv[i] = 0.f; }
+    if (active) {
+      ld_vec<VPT>(xs + t * E + lane * VPT, xv);
+      ld_vec<VPT>(g + (long long)t * gstride + lane * VPT, gv);
+    }
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) dot = fmaf(xv[i], gv[i], dot);
+    dot = allreduce_warp(dot);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) gv[i] = xv[i] * (gv[i] - dot);
+    if (active) st_vec<VPT>(reinterpret_cast<TIO*>(grow0 + t * row_stride_bytes) + lane * VPT, gv);
+  }
+}
+
 }  // namespace srwm

@@ -48,6 +48,13 @@
   X(64, 1, 256, 8, 16, true, 1)  \
   X(64, 2, 128, 8, 16, false, 2)
 
+// Backward with the state detached at every step (W_y and its gradient only)
+#define SRWM_BWD_DET_CONFIGS(X)  \
+  X(8, 0, 32, 2, 16, true, 8)    \
+  X(16, 0, 32, 4, 16, true, 8)   \
+  X(32, 0, 64, 8, 16, true, 6)   \
+  X(64, 0, 128, 16, 16, true, 4)
+
 #define DELTA_FWD_CONFIGS(X)     \
   X(8, 0, 32, 2, 16, true, 8)    \
   X(16, 0, 32, 4, 16, true, 8)   \

@@ -12,8 +12,23 @@ typedef __nv_bfloat16 TIO;
 typedef float TIO;
 #endif
 
-template <int E, int P, int R, int T, bool PK, int MINB>
+// The extended form of a call runs the EXT instantiation of the default configuration.
+constexpr unsigned EXT_FLAGS = F_INPUT_SOFTMAX | F_BASE;
+
+template <int E, int V, int P, int R, int T, bool PK, int MINB>
 int run(const SrwmBwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
+  if (p.flags & EXT_FLAGS) {
+    if constexpr (V == 0) {
+      constexpr int smem = SrwmBwdSmem<TIO, E, P, T, true>::TOTAL;
+      if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; }
+      if (describe_only) return 0;
+      static unsigned long long dev_mask_ext = 0;
+      return launch_kernel(srwm_bwd_kernel<TIO, E, P, R, T, PK, MINB, true>, p, grid, P, smem, s, &dev_mask_ext,
+                           cuda_err);
+    } else {
+      return -6;
+    }
+  }
   constexpr int smem = SrwmBwdSmem<TIO, E, P, T>::TOTAL;
   if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; }
   if (describe_only) return 0;
@@ -31,7 +46,7 @@ int dispatch_srwm_bwd_f32(
     int E, int variant, const SrwmBwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only,
     int* cuda_err) {
 #define X(E_, V_, P_, R_, T_, PK_, MINB_) \
-  if (E == E_ && variant == V_) return run<E_, P_, R_, T_, PK_, MINB_>(p, grid, s, info, describe_only, cuda_err);
+  if (E == E_ && variant == V_) return run<E_, V_, P_, R_, T_, PK_, MINB_>(p, grid, s, info, describe_only, cuda_err);
   SRWM_BWD_CONFIGS(X)
 #undef X
   return (E == 8 || E == 16 || E == 32 || E == 64) ? -6 : -3;

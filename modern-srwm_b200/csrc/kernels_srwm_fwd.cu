@@ -12,8 +12,24 @@ typedef __nv_bfloat16 TIO;
 typedef float TIO;
 #endif
 
-template <int E, int P, int R, int T, bool PK, int MINB>
+// The extended form of a call (flag bits above the ABI's three) runs the EXT instantiation
+// of the default configuration; the plain form keeps its own, unchanged code.
+constexpr unsigned EXT_FLAGS = F_INPUT_SOFTMAX | F_BASE | F_SHIFT_IN | F_DONE;
+
+template <int E, int V, int P, int R, int T, bool PK, int MINB>
 int run(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
+  if (p.flags & EXT_FLAGS) {
+    if constexpr (V == 0) {
+      constexpr int smem = SrwmFwdSmem<TIO, E, T, true>::TOTAL;
+      if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; }
+      if (describe_only) return 0;
+      static unsigned long long dev_mask_ext = 0;
+      return launch_kernel(srwm_fwd_kernel<TIO, E, P, R, T, PK, MINB, true>, p, grid, P, smem, s, &dev_mask_ext,
+                           cuda_err);
+    } else {
+      return -6;
+    }
+  }
   constexpr int smem = SrwmFwdSmem<TIO, E, T>::TOTAL;
   if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; }
   if (describe_only) return 0;
@@ -21,8 +37,20 @@ int run(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int 
   return launch_kernel(srwm_fwd_kernel<TIO, E, P, R, T, PK, MINB>, p, grid, P, smem, s, &dev_mask, cuda_err);
 }
 
-template <int E, int T, bool PK, int MINB, bool DPRE, int NRP>
+template <int E, int V, int T, bool PK, int MINB, bool DPRE, int NRP>
 int run_col(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
+  if (p.flags & EXT_FLAGS) {
+    if constexpr (V == 0) {
+      constexpr int smem = SrwmFwdColSmem<TIO, E, T, true>::TOTAL;
+      if (info) { info->P = 96; info->R = E / NRP; info->T = T; info->smem = smem; }
+      if (describe_only) return 0;
+      static unsigned long long dev_mask_ext = 0;
+      return launch_kernel(srwm_fwd_col_kernel<TIO, E, T, PK, MINB, DPRE, NRP, true>, p, grid, 96, smem, s,
+                           &dev_mask_ext, cuda_err);
+    } else {
+      return -6;
+    }
+  }
   constexpr int smem = SrwmFwdColSmem<TIO, E, T>::TOTAL;
   if (info) { info->P = 96; info->R = E / NRP; info->T = T; info->smem = smem; }
   if (describe_only) return 0;
@@ -40,11 +68,11 @@ int dispatch_srwm_fwd_f32(
     int E, int variant, const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only,
     int* cuda_err) {
 #define X(E_, V_, P_, R_, T_, PK_, MINB_) \
-  if (E == E_ && variant == V_) return run<E_, P_, R_, T_, PK_, MINB_>(p, grid, s, info, describe_only, cuda_err);
+  if (E == E_ && variant == V_) return run<E_, V_, P_, R_, T_, PK_, MINB_>(p, grid, s, info, describe_only, cuda_err);
   SRWM_FWD_CONFIGS(X)
 #undef X
 #define Y(E_, V_, T_, PK_, MINB_, DPRE_, NRP_) \
-  if (E == E_ && variant == V_) return run_col<E_, T_, PK_, MINB_, DPRE_, NRP_>(p, grid, s, info, describe_only, cuda_err);
+  if (E == E_ && variant == V_) return run_col<E_, V_, T_, PK_, MINB_, DPRE_, NRP_>(p, grid, s, info, describe_only, cuda_err);
   SRWM_FWD_COL_CONFIGS(Y)
 #undef Y
   return (E == 8 || E == 16 || E == 32 || E == 64) ? -6 : -3;

@@ -6,7 +6,7 @@
 
 namespace srwm {
 
-enum Op { OP_SRWM_FWD = 0, OP_SRWM_BWD = 1, OP_DELTA_FWD = 2, OP_DELTA_BWD = 3 };
+enum Op { OP_SRWM_FWD = 0, OP_SRWM_BWD = 1, OP_DELTA_FWD = 2, OP_DELTA_BWD = 3, OP_SRWM_BWD_DET = 4 };
 
 // What a (op, E, dtype, variant) combination resolves to.
 struct KernelInfo {
@@ -24,6 +24,7 @@ struct KernelInfo {
                            KernelInfo* info, int describe_only, int* cuda_err);
 SRWM_DECL_DISPATCH(srwm_fwd, SrwmFwdParams)
 SRWM_DECL_DISPATCH(srwm_bwd, SrwmBwdParams)
+SRWM_DECL_DISPATCH(srwm_bwd_det, SrwmBwdDetParams)
 SRWM_DECL_DISPATCH(delta_fwd, DeltaFwdParams)
 SRWM_DECL_DISPATCH(delta_bwd, DeltaBwdParams)
 #undef SRWM_DECL_DISPATCH

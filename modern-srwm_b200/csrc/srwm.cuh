@@ -19,11 +19,26 @@
 
 namespace srwm {
 
+// The extended (layer-level) form of a call, selected by flag bits (common.cuh):
+//   F_INPUT_SOFTMAX  x holds raw activations; the kernels apply softmax over the head dimension
+//                    (supervised_learning/layer.py:162-163, reinforcement_learning/torchbeast/layer.py:383)
+//                    and the backward returns the gradient with respect to the raw values
+//   F_BASE           the state is base + shift, base being the un-repeated slow weights
+//                    ([1,H,E,.], batch stride 0): W_* then receive the final SHIFT W_L - base
+//                    (the subtraction of layer.py:412-415 / :200-204), and the backward reads W_L as
+//                    base + W_*
+//   F_SHIFT_IN       with F_BASE: the initial shift comes from s* (else it is zero)
+//   F_DONE           with F_BASE: done[n, t] != 0 resets the shift of sample n to zero before step t
+//                    (reinforcement_learning/torchbeast_procgen/model.py:1180-1194)
 struct SrwmFwdParams {
   int N, H, L;
   unsigned flags;
   SeqView x, out, q, k, beta, yd, qd, kd, bd;
   StateView Wy, Wq, Wk, wb;
+  StateView bWy, bWq, bWk, bwb;   // slow weights
+  StateView sWy, sWq, sWk, swb;   // initial shift
+  const unsigned char* done;      // [N, L] bytes
+  long long done_sn, done_sl;
 };
 
 struct SrwmBwdParams {
@@ -31,6 +46,7 @@ struct SrwmBwdParams {
   unsigned flags;
   SeqView x, q, k, beta, yd, qd, kd, bd, gout, gx;
   StateView Wy, Wq, Wk, wb, gWy, gWq, gWk, gwb;
+  StateView bWy, bWq, bWk, bwb;   // slow weights
 };
 
 template <int E, int C, int R, int NRG>
@@ -42,6 +58,44 @@ __device__ __forceinline__ void load_tile(const float* g, int rg, int cg, u64 (&
     ld_vec<C>(g + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
 #pragma unroll
     for (int j = 0; j < C; ++j) W[i2][j] = pack2(a[j], b[j]);
+  }
+}
+// W = a + b (b may be null)
+template <int E, int C, int R, int NRG>
+__device__ __forceinline__ void load_tile_sum(const float* ga, const float* gb, int rg, int cg, u64 (&W)[R / 2][C]) {
+#pragma unroll
+  for (int i2 = 0; i2 < R / 2; ++i2) {
+    float a[C], b[C];
+    ld_vec<C>(ga + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
+    ld_vec<C>(ga + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
+    if (gb) {
+      float a1[C], b1[C];
+      ld_vec<C>(gb + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a1);
+      ld_vec<C>(gb + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b1);
+#pragma unroll
+      for (int j = 0; j < C; ++j) { a[j] += a1[j]; b[j] += b1[j]; }
+    }
+#pragma unroll
+    for (int j = 0; j < C; ++j) W[i2][j] = pack2(a[j], b[j]);
+  }
+}
+// g = W - base (base may be null)
+template <int E, int C, int R, int NRG>
+__device__ __forceinline__ void store_tile_diff(float* g, const float* gbase, int rg, int cg, const u64 (&W)[R / 2][C]) {
+#pragma unroll
+  for (int i2 = 0; i2 < R / 2; ++i2) {
+    float a[C], b[C];
+#pragma unroll
+    for (int j = 0; j < C; ++j) unpack2(W[i2][j], a[j], b[j]);
+    if (gbase) {
+      float a1[C], b1[C];
+      ld_vec<C>(gbase + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a1);
+      ld_vec<C>(gbase + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b1);
+#pragma unroll
+      for (int j = 0; j < C; ++j) { a[j] -= a1[j]; b[j] -= b1[j]; }
+    }
+    st_vec<C>(g + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
+    st_vec<C>(g + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
   }
 }
 template <int E, int C, int R, int NRG>
@@ -59,21 +113,23 @@ __device__ __forceinline__ void store_tile(float* g, int rg, int cg, const u64 (
 // ---------------------------------------------------------------------------------------
 // Forward
 // ---------------------------------------------------------------------------------------
-template <typename TIO, int E, int T>
+template <typename TIO, int E, int T, bool EXT = false>
 struct SrwmFwdSmem {
   static constexpr int ROW_IO = E * (int)sizeof(TIO);
   static constexpr int ROW_F = E * 4;
   static constexpr int IN_BYTES = T * ROW_IO;                       // x of one buffer
+  static constexpr int XF_BYTES = (EXT && sizeof(TIO) != 4) ? T * ROW_F : 0;   // softmax(x) in fp32
   static constexpr int OUT_BYTES = T * ROW_IO + 5 * T * ROW_F + 2 * T * 16;  // y | q k yd qd kd | beta bd
   static constexpr int XCHG_BYTES = 2 * 2 * ROW_F + 2 * 16;         // q~,k~ (x2 parity) + beta (x2)
   static constexpr int WB_BYTES = 4 * ROW_F;                        // w_b transposed [4][E]
-  static constexpr int TOTAL = 2 * IN_BYTES + OUT_BYTES + XCHG_BYTES + WB_BYTES;
+  static constexpr int DONE_BYTES = EXT ? ((T + 15) / 16) * 16 : 0; // reset flags of the chunk
+  static constexpr int TOTAL = 2 * IN_BYTES + XF_BYTES + OUT_BYTES + XCHG_BYTES + WB_BYTES + DONE_BYTES;
 };
 
-template <typename TIO, int E, int P, int R, int T, bool PK, int MINB>
+template <typename TIO, int E, int P, int R, int T, bool PK, int MINB, bool EXT = false>
 __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p) {
   using TL = Tiling<E, P, R>;
-  using SM = SrwmFwdSmem<TIO, E, T>;
+  using SM = SrwmFwdSmem<TIO, E, T, EXT>;
   constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2;
   const int tid = threadIdx.x;
   const int rg = tid % NRG, cg = tid / NRG;
@@ -83,7 +139,8 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
   const int jb = (cg % TL::BETA_CG_STEP == 0) ? cg / TL::BETA_CG_STEP : -1;
 
   extern __shared__ __align__(16) unsigned char smem[];
-  unsigned char* s_o = smem + 2 * SM::IN_BYTES;
+  float* xf32 = reinterpret_cast<float*>(smem + 2 * SM::IN_BYTES);   // EXT, bf16 streams only
+  unsigned char* s_o = smem + 2 * SM::IN_BYTES + SM::XF_BYTES;
   TIO* sy = reinterpret_cast<TIO*>(s_o);
   float* sq = reinterpret_cast<float*>(s_o + T * SM::ROW_IO);
   float* sk = sq + T * E;
@@ -95,16 +152,31 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
   float* xq = sbd + T * 4;             // [2][2][E]  pre-softmax q~ / k~, double buffered
   float* xbeta = xq + 4 * E;           // [2][4]
   float* wbT = xbeta + 8;              // [4][E]
+  unsigned char* sdone = reinterpret_cast<unsigned char*>(wbT + 4 * E);   // [T] (EXT)
+
+  const bool smx = EXT && (p.flags & F_INPUT_SOFTMAX);
+  const bool has_base = EXT && (p.flags & F_BASE);
+  const bool has_done = EXT && (p.flags & F_DONE);
 
   u64 Wy[R2][C], Wq[R2][C], Wk[R2][C];
   float* gWy = p.Wy.mat(n, h);
   float* gWq = p.Wq.mat(n, h);
   float* gWk = p.Wk.mat(n, h);
   float* gwb = p.wb.mat(n, h);
-  load_tile<E, C, R, NRG>(gWy, rg, cg, Wy);
-  load_tile<E, C, R, NRG>(gWq, rg, cg, Wq);
-  load_tile<E, C, R, NRG>(gWk, rg, cg, Wk);
-  for (int i = tid; i < 4 * E; i += P) wbT[(i % 4) * E + i / 4] = gwb[i];   // [E][4] -> [4][E]
+  if (has_base) {
+    const bool sh = (p.flags & F_SHIFT_IN) != 0;
+    load_tile_sum<E, C, R, NRG>(p.bWy.mat(n, h), sh ? p.sWy.mat(n, h) : nullptr, rg, cg, Wy);
+    load_tile_sum<E, C, R, NRG>(p.bWq.mat(n, h), sh ? p.sWq.mat(n, h) : nullptr, rg, cg, Wq);
+    load_tile_sum<E, C, R, NRG>(p.bWk.mat(n, h), sh ? p.sWk.mat(n, h) : nullptr, rg, cg, Wk);
+    const float* bb = p.bwb.mat(n, h);
+    const float* sb = sh ? p.swb.mat(n, h) : nullptr;
+    for (int i = tid; i < 4 * E; i += P) wbT[(i % 4) * E + i / 4] = bb[i] + (sb ? sb[i] : 0.f);
+  } else {
+    load_tile<E, C, R, NRG>(gWy, rg, cg, Wy);
+    load_tile<E, C, R, NRG>(gWq, rg, cg, Wq);
+    load_tile<E, C, R, NRG>(gWk, rg, cg, Wk);
+    for (int i = tid; i < 4 * E; i += P) wbT[(i % 4) * E + i / 4] = gwb[i];   // [E][4] -> [4][E]
+  }
 
   const int L = p.L;
   const int nchunks = (L + T - 1) / T;
@@ -115,22 +187,54 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
   };
   stage_chunk(0);
   cp_async_commit();
+  // reset flags travel one chunk ahead in a register
+  int dn_next = 0;
+  if (has_done && tid < min(T, L)) dn_next = p.done[(long long)n * p.done_sn + (long long)tid * p.done_sl];
 
   int par = 0;
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * T, nt = min(T, L - t0);
     if (c + 1 < nchunks) stage_chunk(c + 1);
     cp_async_commit();
+    if (has_done) {
+      if (tid < T) sdone[tid] = (unsigned char)dn_next;
+      if (tid < min(T, L - t0 - T))
+        dn_next = p.done[(long long)n * p.done_sn + (long long)(t0 + T + tid) * p.done_sl];
+    }
     cp_async_wait<1>();
     __syncthreads();   // chunk c (and, first time, w_b) visible; output stage free again
     const TIO* sx = in_buf(c & 1);
+    const float* sxs = nullptr;   // softmax(x) of this chunk, when the kernel applies it
+    if constexpr (EXT) {
+      if (smx) {
+        float* d = sizeof(TIO) == 4 ? reinterpret_cast<float*>(in_buf(c & 1)) : xf32;
+        softmax_rows<TIO, E, P>(sx, d, nt, tid);
+        __syncthreads();
+        sxs = d;
+      }
+    }
 
     #pragma unroll 1
 
     for (int t = 0; t < nt; ++t, par ^= 1) {
+      if constexpr (EXT) {
+        if (has_done && sdone[t]) {   // episode boundary: the shift goes back to zero
+          load_tile<E, C, R, NRG>(p.bWy.mat(n, h), rg, cg, Wy);
+          load_tile<E, C, R, NRG>(p.bWq.mat(n, h), rg, cg, Wq);
+          load_tile<E, C, R, NRG>(p.bWk.mat(n, h), rg, cg, Wk);
+          if (jb >= 0) {
+            const float* bb = p.bwb.mat(n, h);
+            float wr0[R];
+#pragma unroll
+            for (int i = 0; i < R; ++i) wr0[i] = bb[row_of<R, NRG>(rg, i) * 4 + jb];
+            st_rows<R, NRG>(wbT + jb * E, rg, wr0);
+          }
+        }
+      }
       // ---- pass 1: [y, q~, k~, b~] = x.W ------------------------------------------------
       float xr[R];
-      ld_rows<R, NRG>(sx + t * E, rg, xr);
+      if (EXT && sxs) ld_rows<R, NRG>(sxs + t * E, rg, xr);
+      else ld_rows<R, NRG>(sx + t * E, rg, xr);
       u64 ay[C], aq[C], ak[C];
 #pragma unroll
       for (int j = 0; j < C; ++j) { ay[j] = 0ull; aq[j] = 0ull; ak[j] = 0ull; }
@@ -272,11 +376,20 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
     }
   }
 
-  store_tile<E, C, R, NRG>(gWy, rg, cg, Wy);
-  store_tile<E, C, R, NRG>(gWq, rg, cg, Wq);
-  store_tile<E, C, R, NRG>(gWk, rg, cg, Wk);
+  if (has_base) {   // W_* receive the shift W_L - base
+    store_tile_diff<E, C, R, NRG>(gWy, p.bWy.mat(n, h), rg, cg, Wy);
+    store_tile_diff<E, C, R, NRG>(gWq, p.bWq.mat(n, h), rg, cg, Wq);
+    store_tile_diff<E, C, R, NRG>(gWk, p.bWk.mat(n, h), rg, cg, Wk);
+  } else {
+    store_tile<E, C, R, NRG>(gWy, rg, cg, Wy);
+    store_tile<E, C, R, NRG>(gWq, rg, cg, Wq);
+    store_tile<E, C, R, NRG>(gWk, rg, cg, Wk);
+  }
   __syncthreads();
-  for (int i = tid; i < 4 * E; i += P) gwb[i] = wbT[(i % 4) * E + i / 4];
+  {
+    const float* bb = has_base ? p.bwb.mat(n, h) : nullptr;
+    for (int i = tid; i < 4 * E; i += P) gwb[i] = wbT[(i % 4) * E + i / 4] - (bb ? bb[i] : 0.f);
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -289,7 +402,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
 // meanwhile handles the four w_b columns (lane = column j x an eighth of the rows).
 // One block-wide barrier per step (q, k, beta published through the output staging rows).
 // ---------------------------------------------------------------------------------------
-template <typename TIO, int E, int T>
+template <typename TIO, int E, int T, bool EXT = false>
 struct SrwmFwdColSmem {
   static constexpr int ROW_IO = E * (int)sizeof(TIO);
   static constexpr int ROW_F = E * 4;
@@ -298,23 +411,18 @@ struct SrwmFwdColSmem {
   static constexpr int OUT_BYTES = T * ROW_IO + 5 * T * ROW_F + 2 * T * 16;
   static constexpr int WB_BYTES = 4 * ROW_F;
   static constexpr int DQ_BYTES = 2 * ROW_F;                          // q - k, double buffered
-  static constexpr int TOTAL = 2 * IN_BYTES + XF_BYTES + OUT_BYTES + WB_BYTES + DQ_BYTES;
+  static constexpr int DONE_BYTES = EXT ? ((T + 15) / 16) * 16 : 0;   // reset flags of the chunk
+  static constexpr int TOTAL = 2 * IN_BYTES + XF_BYTES + OUT_BYTES + WB_BYTES + DQ_BYTES + DONE_BYTES;
 };
 
-__device__ __forceinline__ float warp_max(float v) {
-  float r;
-  asm volatile("redux.sync.max.f32 %0, %1, 0xffffffff;" : "=f"(r) : "f"(v));
-  return r;
-}
-
-template <typename TIO, int E, int T, bool PK, int MINB, bool DPRE, int NRP>
+template <typename TIO, int E, int T, bool PK, int MINB, bool DPRE, int NRP, bool EXT = false>
 __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdParams p) {
   static_assert(E == 16 || E == 32 || E == 64, "column layout: one warp per block");
   // Lane (cq, rp) of a warp holds CPL adjacent columns x RL rows (row part rp of NRP) of the
   // warp's block.  NRP = 1 is the pure column layout; NRP > 1 trades a log2(NRP)-stage
   // shuffle per pass for 1/NRP of the broadcast operand loads (the shared-memory data pipe
   // is the busiest unit of this kernel).
-  using SM = SrwmFwdColSmem<TIO, E, T>;
+  using SM = SrwmFwdColSmem<TIO, E, T, EXT>;
   // At E = 16 a block has only 16 columns: NRP = 2 with one column per lane, and the two
   // row-part lanes of a column both end up holding its (duplicated) pre-activation (DUP).
   constexpr int P = 96, CPL = (E * NRP) / 32, RL = E / NRP, RL2 = RL / 2, RB = E / 8;
@@ -342,24 +450,51 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
   float* sbd = sbeta + T * 4;   // [T][4]
   float* wbT = sbd + T * 4;     // [4][E]
   float* sdq = wbT + 4 * E;     // [2][E]  q - k of the current step (DPRE)
+  unsigned char* sdone = reinterpret_cast<unsigned char*>(sdq + 2 * E);   // [T] (EXT)
   float* sdz = warp == 0 ? syd : (warp == 1 ? sqd : skd);
+
+  const bool smx = EXT && (p.flags & F_INPUT_SOFTMAX);
+  const bool has_base = EXT && (p.flags & F_BASE);
+  const bool has_done = EXT && (p.flags & F_DONE);
 
   u64 W[RL2][CPL];
   float* gW = (warp == 0 ? p.Wy : (warp == 1 ? p.Wq : p.Wk)).mat(n, h);
   float* gwb = p.wb.mat(n, h);
+  // slow weights / initial shift of this warp's block (extended form)
+  const float* gB = has_base ? (warp == 0 ? p.bWy : (warp == 1 ? p.bWq : p.bWk)).mat(n, h) : nullptr;
+  const float* gS = (has_base && (p.flags & F_SHIFT_IN)) ? (warp == 0 ? p.sWy : (warp == 1 ? p.sWq : p.sWk)).mat(n, h)
+                                                         : nullptr;
   // local row r of row part rp is global row ((r/4)*NRP + rp)*4 + r%4: quads of rows are
   // interleaved over the row parts, so the lanes of a warp read an operand vector as adjacent
   // 16-byte pieces (no shared-memory bank conflict between row parts)
   auto grow = [&](int r) { return ((r / 4) * NRP + rp) * 4 + (r % 4); };
+  // W = ga + gb (gb may be null)
+  auto load_state = [&](const float* ga, const float* gb) {
 #pragma unroll
-  for (int e2 = 0; e2 < RL2; ++e2) {
-    float a[CPL], b[CPL];
-    ld_vec<CPL>(gW + grow(2 * e2) * E + c0, a);
-    ld_vec<CPL>(gW + grow(2 * e2 + 1) * E + c0, b);
+    for (int e2 = 0; e2 < RL2; ++e2) {
+      float a[CPL], b[CPL];
+      ld_vec<CPL>(ga + grow(2 * e2) * E + c0, a);
+      ld_vec<CPL>(ga + grow(2 * e2 + 1) * E + c0, b);
+      if (EXT && gb) {
+        float a1[CPL], b1[CPL];
+        ld_vec<CPL>(gb + grow(2 * e2) * E + c0, a1);
+        ld_vec<CPL>(gb + grow(2 * e2 + 1) * E + c0, b1);
 #pragma unroll
-    for (int c = 0; c < CPL; ++c) W[e2][c] = pack2(a[c], b[c]);
+        for (int c = 0; c < CPL; ++c) { a[c] += a1[c]; b[c] += b1[c]; }
+      }
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) W[e2][c] = pack2(a[c], b[c]);
+    }
+  };
+  if (has_base) {
+    load_state(gB, gS);
+    const float* bb = p.bwb.mat(n, h);
+    const float* sb = gS ? p.swb.mat(n, h) : nullptr;
+    for (int i = tid; i < 4 * E; i += P) wbT[(i % 4) * E + i / 4] = bb[i] + (sb ? sb[i] : 0.f);
+  } else {
+    load_state(gW, nullptr);
+    for (int i = tid; i < 4 * E; i += P) wbT[(i % 4) * E + i / 4] = gwb[i];
   }
-  for (int i = tid; i < 4 * E; i += P) wbT[(i % 4) * E + i / 4] = gwb[i];
 
   const int L = p.L;
   const int nchunks = (L + T - 1) / T;
@@ -372,23 +507,32 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
   cp_async_commit();
   const u64 neg1 = pack2(-1.f, -1.f);
   int par = 0;
+  // reset flags travel one chunk ahead in a register
+  int dn_next = 0;
+  if (has_done && tid < min(T, L)) dn_next = p.done[(long long)n * p.done_sn + (long long)tid * p.done_sl];
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * T, nt = min(T, L - t0);
     if (c + 1 < nchunks) stage_chunk(c + 1);
     cp_async_commit();
+    if (has_done) {
+      if (tid < T) sdone[tid] = (unsigned char)dn_next;
+      if (tid < min(T, L - t0 - T))
+        dn_next = p.done[(long long)n * p.done_sn + (long long)(t0 + T + tid) * p.done_sl];
+    }
     cp_async_wait<1>();
     __syncthreads();
     const float* sxf;
     if constexpr (sizeof(TIO) == 4) {
-      sxf = reinterpret_cast<const float*>(in_buf(c & 1));
-    } else {
-      const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(in_buf(c & 1));
-      for (int i = tid; i < nt * E / 2; i += P) {
-        float v[2];
-        ld_vec<2>(xb + 2 * i, v);
-        st_vec<2>(xf32 + 2 * i, v);
+      float* xs = reinterpret_cast<float*>(in_buf(c & 1));
+      if (smx) {
+        softmax_rows<TIO, E, P>(xs, xs, nt, tid);
+        __syncthreads();
       }
+      sxf = xs;
+    } else {
+      if (smx) softmax_rows<TIO, E, P>(in_buf(c & 1), xf32, nt, tid);
+      else convert_rows<TIO, E, P>(in_buf(c & 1), xf32, nt, tid);
       __syncthreads();
       sxf = xf32;
     }
@@ -396,6 +540,16 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
     #pragma unroll 1
 
     for (int t = 0; t < nt; ++t, par ^= 1) {
+      if constexpr (EXT) {
+        if (has_done && sdone[t]) {   // episode boundary: the shift goes back to zero
+          load_state(gB, nullptr);
+          if (warp == 0) {
+            const float* bb = p.bwb.mat(n, h);
+#pragma unroll
+            for (int i = 0; i < RB; ++i) wbT[jb * E + r8 * RB + i] = bb[(r8 * RB + i) * 4 + jb];
+          }
+        }
+      }
       const float* xr = sxf + t * E;
       const float* qr = sq + t * E;
       const float* kr = sk + t * E;
@@ -544,11 +698,21 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
     float a[CPL], b[CPL];
 #pragma unroll
     for (int cc = 0; cc < CPL; ++cc) unpack2(W[e2][cc], a[cc], b[cc]);
+    if (EXT && gB) {   // W_* receive the shift W_L - base
+      float a1[CPL], b1[CPL];
+      ld_vec<CPL>(gB + grow(2 * e2) * E + c0, a1);
+      ld_vec<CPL>(gB + grow(2 * e2 + 1) * E + c0, b1);
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) { a[cc] -= a1[cc]; b[cc] -= b1[cc]; }
+    }
     st_vec<CPL>(gW + grow(2 * e2) * E + c0, a);
     st_vec<CPL>(gW + grow(2 * e2 + 1) * E + c0, b);
   }
   __syncthreads();
-  for (int i = tid; i < 4 * E; i += P) gwb[i] = wbT[(i % 4) * E + i / 4];
+  {
+    const float* bb = has_base ? p.bwb.mat(n, h) : nullptr;
+    for (int i = tid; i < 4 * E; i += P) gwb[i] = wbT[(i % 4) * E + i / 4] - (bb ? bb[i] : 0.f);
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -563,7 +727,7 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
 // barrier; phase 2 finishes the step.  gx is an output only: its per-warp partials are
 // parked in shared memory and summed when the chunk is written out.
 // ---------------------------------------------------------------------------------------
-template <typename TIO, int E, int P, int T>
+template <typename TIO, int E, int P, int T, bool EXT = false>
 struct SrwmBwdSmem {
   static constexpr int NWARP = P / 32;
   static constexpr int ROW_IO = E * (int)sizeof(TIO);
@@ -574,13 +738,14 @@ struct SrwmBwdSmem {
   static constexpr int XROW_BYTES = 2 * NWARP * 2 * ROW_F;       // [2 parity][NWARP][gq,gk][E]
   static constexpr int XSC_BYTES = 2 * NWARP * 8 * 4;            // [2][NWARP][8] scalars
   static constexpr int WB_BYTES = 2 * 4 * ROW_F;                 // w_b^T and its gradient
-  static constexpr int TOTAL = 2 * IN_BYTES + GX_BYTES + XROW_BYTES + XSC_BYTES + WB_BYTES;
+  static constexpr int XF_BYTES = (EXT && sizeof(TIO) != 4) ? T * ROW_F : 0;   // x (or softmax(x)) in fp32
+  static constexpr int TOTAL = 2 * IN_BYTES + GX_BYTES + XROW_BYTES + XSC_BYTES + WB_BYTES + XF_BYTES;
 };
 
-template <typename TIO, int E, int P, int R, int T, bool PK, int MINB>
+template <typename TIO, int E, int P, int R, int T, bool PK, int MINB, bool EXT = false>
 __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p) {
   using TL = Tiling<E, P, R>;
-  using SM = SrwmBwdSmem<TIO, E, P, T>;
+  using SM = SrwmBwdSmem<TIO, E, P, T, EXT>;
   constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2, NWARP = TL::NWARP, CGW = TL::CGW;
   // Row sums and scalars leave the warp through reduce-scatters when the tile shape allows
   // it (every lane ends up with a distinct piece); otherwise through butterfly all-reduces.
@@ -610,15 +775,25 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
   float* xsc = reinterpret_cast<float*>(s_o + SM::GX_BYTES + SM::XROW_BYTES);  // [2][NWARP][8]
   float* wbT = xsc + 2 * NWARP * 8;                                         // [4][E]
   float* gbT = wbT + 4 * E;                                                 // [4][E]
+  float* xf32 = gbT + 4 * E;                                                // [T][E] (EXT, bf16 streams)
+
+  const bool smx = EXT && (p.flags & F_INPUT_SOFTMAX);
+  const bool has_base = EXT && (p.flags & F_BASE);
 
   u64 Wy[R2][C], Wq[R2][C], Wk[R2][C], Gy[R2][C], Gq[R2][C], Gk[R2][C];
   float* gWy = p.Wy.mat(n, h);
   float* gWq = p.Wq.mat(n, h);
   float* gWk = p.Wk.mat(n, h);
   float* gwb = p.wb.mat(n, h);
-  load_tile<E, C, R, NRG>(gWy, rg, cg, Wy);
-  load_tile<E, C, R, NRG>(gWq, rg, cg, Wq);
-  load_tile<E, C, R, NRG>(gWk, rg, cg, Wk);
+  if (has_base) {   // W_* hold the final shift: W_L = base + shift
+    load_tile_sum<E, C, R, NRG>(gWy, p.bWy.mat(n, h), rg, cg, Wy);
+    load_tile_sum<E, C, R, NRG>(gWq, p.bWq.mat(n, h), rg, cg, Wq);
+    load_tile_sum<E, C, R, NRG>(gWk, p.bWk.mat(n, h), rg, cg, Wk);
+  } else {
+    load_tile<E, C, R, NRG>(gWy, rg, cg, Wy);
+    load_tile<E, C, R, NRG>(gWq, rg, cg, Wq);
+    load_tile<E, C, R, NRG>(gWk, rg, cg, Wk);
+  }
   const bool gin = (p.flags & 2u) != 0;
   if (gin) {
     load_tile<E, C, R, NRG>(p.gWy.mat(n, h), rg, cg, Gy);
@@ -632,8 +807,9 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
   }
   {
     const float* ggwb = p.gwb.mat(n, h);
+    const float* bb = has_base ? p.bwb.mat(n, h) : nullptr;
     for (int i = tid; i < 4 * E; i += P) {
-      wbT[(i % 4) * E + i / 4] = gwb[i];
+      wbT[(i % 4) * E + i / 4] = gwb[i] + (bb ? bb[i] : 0.f);
       gbT[(i % 4) * E + i / 4] = gin ? ggwb[i] : 0.f;
     }
   }
@@ -667,8 +843,23 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
     cp_async_wait<1>();
     __syncthreads();
 
-    const unsigned char* ib = in_buf(c & 1);
+    unsigned char* ib = in_buf(c & 1);
     const TIO* sx = reinterpret_cast<const TIO*>(ib);
+    // in the extended form x is read as fp32 rows: softmax(x) when the kernel applies it
+    const float* sxs = reinterpret_cast<const float*>(ib);
+    if constexpr (EXT) {
+      if constexpr (sizeof(TIO) == 4) {
+        if (smx) {
+          softmax_rows<TIO, E, P>(sx, reinterpret_cast<float*>(ib), nt, tid);
+          __syncthreads();
+        }
+      } else {
+        if (smx) softmax_rows<TIO, E, P>(sx, xf32, nt, tid);
+        else convert_rows<TIO, E, P>(sx, xf32, nt, tid);
+        __syncthreads();
+        sxs = xf32;
+      }
+    }
     const TIO* sg = reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO);
     const float* sq = reinterpret_cast<const float*>(ib + 2 * T * SM::ROW_IO);
     const float* sk = sq + T * E;
@@ -914,7 +1105,8 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         for (int w = 0; w < NWARP; ++w) sc[0] += xsc[(par * NWARP + w) * 8 + jb];
       }
       float xr[R];
-      ld_rows<R, NRG>(sx + t * E, rg, xr);
+      if constexpr (EXT) ld_rows<R, NRG>(sxs + t * E, rg, xr);
+      else ld_rows<R, NRG>(sx + t * E, rg, xr);
       u64 gx2[R2], x2[R2];
 #pragma unroll
       for (int i2 = 0; i2 < R2; ++i2) {
@@ -976,7 +1168,15 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
 #pragma unroll
         for (int u = 0; u < 4; ++u) acc[u] += v[u];
       }
-      st_vec<4>(reinterpret_cast<TIO*>(p.gx.row(n, h, t0 + t)) + e4 * 4, acc);
+      if (EXT && smx) st_vec<4>(sgx + (t * NWARP) * E + e4 * 4, acc);   // finished below, through the softmax
+      else st_vec<4>(reinterpret_cast<TIO*>(p.gx.row(n, h, t0 + t)) + e4 * 4, acc);
+    }
+    if constexpr (EXT) {
+      if (smx) {
+        __syncthreads();
+        softmax_bwd_rows<TIO, E, P>(sxs, sgx, NWARP * E, p.gx.row(n, h, t0), p.gx.sl, nt, tid);
+        __syncthreads();   // softmax(x) may sit in the staging buffer the next prefetch overwrites
+      }
     }
   }
 
@@ -985,19 +1185,185 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
   store_tile<E, C, R, NRG>(p.gWq.mat(n, h), rg, cg, Gq);
   store_tile<E, C, R, NRG>(p.gWk.mat(n, h), rg, cg, Gk);
   const bool restore = (p.flags & 4u) != 0;
-  if (restore) {
-    store_tile<E, C, R, NRG>(gWy, rg, cg, Wy);
-    store_tile<E, C, R, NRG>(gWq, rg, cg, Wq);
-    store_tile<E, C, R, NRG>(gWk, rg, cg, Wk);
+  if (restore) {   // W_0, or the initial shift W_0 - base in the extended form
+    store_tile_diff<E, C, R, NRG>(gWy, has_base ? p.bWy.mat(n, h) : nullptr, rg, cg, Wy);
+    store_tile_diff<E, C, R, NRG>(gWq, has_base ? p.bWq.mat(n, h) : nullptr, rg, cg, Wq);
+    store_tile_diff<E, C, R, NRG>(gWk, has_base ? p.bWk.mat(n, h) : nullptr, rg, cg, Wk);
   }
   __syncthreads();
   {
     float* ggwb = p.gwb.mat(n, h);
+    const float* bb = has_base ? p.bwb.mat(n, h) : nullptr;
     for (int i = tid; i < 4 * E; i += P) {
       ggwb[i] = gbT[(i % 4) * E + i / 4];
-      if (restore) gwb[i] = wbT[(i % 4) * E + i / 4];
+      if (restore) gwb[i] = wbT[(i % 4) * E + i / 4] - (bb ? bb[i] : 0.f);
     }
   }
+}
+
+// ---------------------------------------------------------------------------------------
+// Backward with the state detached at every step.  The reinforcement-learning learner calls
+// the layer one step at a time and detaches the state it carries
+// (reinforcement_learning/torchbeast/layer.py:412-421 under the loop of
+// reinforcement_learning/torchbeast_procgen/model.py:1180-1197), so only
+// out_t = x_t.W_y(t-1) carries gradient:
+//   gx_t = W_y(t-1) g_t  (then through the input softmax) ,  G_y += x_t^T g_t ,
+// and W_q, W_k, w_b receive none.  W_y(t-1) is replayed FORWARD in time from base + shift
+// with the saved k, beta_y, d_y (W_y += k^T (b_y d_y)), going back to base where done is set.
+// No step waits on another step's reductions: the gx partials are parked per warp and
+// combined once per chunk, so the kernel has no barrier inside the time loop.
+// ---------------------------------------------------------------------------------------
+struct SrwmBwdDetParams {
+  int N, H, L;
+  unsigned flags;                 // F_INPUT_SOFTMAX, F_SHIFT_IN, F_DONE
+  SeqView x, k, beta, yd, gout, gx;
+  StateView bWy, sWy, gWy;        // initial W_y = bWy (+ sWy); gWy receives sum_t x_t^T g_t
+  const unsigned char* done;
+  long long done_sn, done_sl;
+};
+
+template <typename TIO, int E, int P, int T>
+struct SrwmBwdDetSmem {
+  static constexpr int NWARP = P / 32;
+  static constexpr int ROW_IO = E * (int)sizeof(TIO);
+  static constexpr int ROW_F = E * 4;
+  static constexpr int IN_BYTES = 2 * T * ROW_IO + 2 * T * ROW_F + T * 16;   // x, gout | k, yd | beta
+  static constexpr int GX_BYTES = T * NWARP * ROW_F;
+  static constexpr int XF_BYTES = sizeof(TIO) != 4 ? T * ROW_F : 0;
+  static constexpr int DONE_BYTES = ((T + 15) / 16) * 16;
+  static constexpr int TOTAL = 2 * IN_BYTES + GX_BYTES + XF_BYTES + DONE_BYTES;
+};
+
+template <typename TIO, int E, int P, int R, int T, bool PK, int MINB>
+__global__ void __launch_bounds__(P, MINB) srwm_bwd_det_kernel(const SrwmBwdDetParams p) {
+  using TL = Tiling<E, P, R>;
+  using SM = SrwmBwdDetSmem<TIO, E, P, T>;
+  constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2, NWARP = TL::NWARP;
+  const int tid = threadIdx.x;
+  const int rg = tid % NRG, cg = tid / NRG;
+  const int warp = tid / 32, lane = tid % 32;
+  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
+  const bool smx = (p.flags & F_INPUT_SOFTMAX) != 0;
+  const bool has_done = (p.flags & F_DONE) != 0;
+
+  extern __shared__ __align__(16) unsigned char smem[];
+  float* sgx = reinterpret_cast<float*>(smem + 2 * SM::IN_BYTES);           // [T][NWARP][E]
+  float* xf32 = reinterpret_cast<float*>(smem + 2 * SM::IN_BYTES + SM::GX_BYTES);
+  unsigned char* sdone = smem + 2 * SM::IN_BYTES + SM::GX_BYTES + SM::XF_BYTES;
+
+  u64 W[R2][C], G[R2][C];
+  const float* gB = p.bWy.mat(n, h);
+  load_tile_sum<E, C, R, NRG>(gB, (p.flags & F_SHIFT_IN) ? p.sWy.mat(n, h) : nullptr, rg, cg, W);
+#pragma unroll
+  for (int i2 = 0; i2 < R2; ++i2)
+#pragma unroll
+    for (int j = 0; j < C; ++j) G[i2][j] = 0ull;
+
+  const int L = p.L;
+  const int nchunks = (L + T - 1) / T;
+  auto in_buf = [&](int b) { return smem + b * SM::IN_BYTES; };
+  auto stage_chunk = [&](int c) {
+    const int t0 = c * T, nt = min(T, L - t0);
+    unsigned char* ib = in_buf(c & 1);
+    stage_rows<SM::ROW_IO, P>(ib, p.x.row(n, h, t0), p.x.sl, nt, tid);
+    stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.gout.row(n, h, t0), p.gout.sl, nt, tid);
+    unsigned char* fb = ib + 2 * T * SM::ROW_IO;
+    stage_rows<SM::ROW_F, P>(fb, p.k.row(n, h, t0), p.k.sl, nt, tid);
+    stage_rows<SM::ROW_F, P>(fb + T * SM::ROW_F, p.yd.row(n, h, t0), p.yd.sl, nt, tid);
+    stage_rows<16, P>(fb + 2 * T * SM::ROW_F, p.beta.row(n, h, t0), p.beta.sl, nt, tid);
+  };
+  stage_chunk(0);
+  cp_async_commit();
+  int dn_next = 0;
+  if (has_done && tid < min(T, L)) dn_next = p.done[(long long)n * p.done_sn + (long long)tid * p.done_sl];
+
+  for (int c = 0; c < nchunks; ++c) {
+    const int t0 = c * T, nt = min(T, L - t0);
+    if (c + 1 < nchunks) stage_chunk(c + 1);
+    cp_async_commit();
+    if (has_done) {
+      if (tid < T) sdone[tid] = (unsigned char)dn_next;
+      if (tid < min(T, L - t0 - T))
+        dn_next = p.done[(long long)n * p.done_sn + (long long)(t0 + T + tid) * p.done_sl];
+    }
+    cp_async_wait<1>();
+    __syncthreads();   // chunk c staged; sgx, xf32 and sdone of the previous chunk no longer read
+
+    unsigned char* ib = in_buf(c & 1);
+    const TIO* sx = reinterpret_cast<const TIO*>(ib);
+    const TIO* sg = reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO);
+    const float* sk = reinterpret_cast<const float*>(ib + 2 * T * SM::ROW_IO);
+    const float* syd = sk + T * E;
+    const float* sbeta = syd + T * E;
+    const float* sxs = reinterpret_cast<const float*>(ib);
+    if constexpr (sizeof(TIO) == 4) {
+      if (smx) {
+        softmax_rows<TIO, E, P>(sx, reinterpret_cast<float*>(ib), nt, tid);
+        __syncthreads();
+      }
+    } else {
+      if (smx) softmax_rows<TIO, E, P>(sx, xf32, nt, tid);
+      else convert_rows<TIO, E, P>(sx, xf32, nt, tid);
+      __syncthreads();
+      sxs = xf32;
+    }
+
+#pragma unroll 1
+    for (int t = 0; t < nt; ++t) {
+      if (has_done && sdone[t]) load_tile<E, C, R, NRG>(gB, rg, cg, W);
+      float xr[R], kr[R], g[C], dz[C];
+      ld_rows<R, NRG>(sxs + t * E, rg, xr);
+      ld_rows<R, NRG>(sk + t * E, rg, kr);
+      ld_vec<C>(sg + t * E + cg * C, g);
+      ld_vec<C>(syd + t * E + cg * C, dz);
+      const float by = sbeta[t * 4];
+      u64 gx2[R2], x2[R2], k2[R2];
+#pragma unroll
+      for (int i2 = 0; i2 < R2; ++i2) {
+        gx2[i2] = 0ull;
+        x2[i2] = pack2(xr[2 * i2], xr[2 * i2 + 1]);
+        k2[i2] = pack2(kr[2 * i2], kr[2 * i2 + 1]);
+      }
+#pragma unroll
+      for (int j = 0; j < C; ++j) {
+        const u64 g2 = dup2(g[j]);
+        const u64 in2 = dup2(by * dz[j]);
+#pragma unroll
+        for (int i2 = 0; i2 < R2; ++i2) {
+          gx2[i2] = fma2<PK>(W[i2][j], g2, gx2[i2]);      // with W_y(t-1)
+          G[i2][j] = fma2<PK>(x2[i2], g2, G[i2][j]);
+          W[i2][j] = fma2<PK>(k2[i2], in2, W[i2][j]);     // the step's update
+        }
+      }
+      float gxr[R];
+#pragma unroll
+      for (int i2 = 0; i2 < R2; ++i2) unpack2(gx2[i2], gxr[2 * i2], gxr[2 * i2 + 1]);
+#pragma unroll
+      for (int i = 0; i < R; ++i) gxr[i] = allreduce_cols<NRG>(gxr[i]);
+      if (lane < NRG) st_rows<R, NRG>(sgx + (t * NWARP + warp) * E, rg, gxr);
+    }
+
+    __syncthreads();
+    for (int idx = tid; idx < nt * (E / 4); idx += P) {
+      const int e4 = idx % (E / 4), t = idx / (E / 4);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int w = 0; w < NWARP; ++w) {
+        float v[4];
+        ld_vec<4>(sgx + (t * NWARP + w) * E + e4 * 4, v);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] += v[u];
+      }
+      if (smx) st_vec<4>(sgx + (t * NWARP) * E + e4 * 4, acc);
+      else st_vec<4>(reinterpret_cast<TIO*>(p.gx.row(n, h, t0 + t)) + e4 * 4, acc);
+    }
+    if (smx) {
+      __syncthreads();
+      softmax_bwd_rows<TIO, E, P>(sxs, sgx, NWARP * E, p.gx.row(n, h, t0), p.gx.sl, nt, tid);
+      __syncthreads();   // softmax(x) may sit in the staging buffer the next prefetch overwrites
+    }
+  }
+  store_tile<E, C, R, NRG>(p.gWy.mat(n, h), rg, cg, G);
 }
 
 }  // namespace srwm

@@ -13,8 +13,9 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libsrwm_b200.so")
 
 F32, BF16 = 0, 1
-FLAG_NO_SAVE, FLAG_STATE_GRAD_IN, FLAG_RESTORE_STATE = 1, 2, 4
-OP_SRWM_FWD, OP_SRWM_BWD, OP_DELTA_FWD, OP_DELTA_BWD = 0, 1, 2, 3
+FLAG_NO_SAVE, FLAG_STATE_GRAD_IN, FLAG_RESTORE_STATE, FLAG_INPUT_SOFTMAX = 1, 2, 4, 8
+OP_SRWM_FWD, OP_SRWM_BWD, OP_DELTA_FWD, OP_DELTA_BWD, OP_SRWM_BWD_DET = 0, 1, 2, 3, 4
+ABI_VERSION = 2
 
 ERR_NULL, ERR_SHAPE, ERR_HEAD_DIM, ERR_DTYPE, ERR_ALIGN, ERR_VARIANT, ERR_CUDA, ERR_TOO_LARGE = (
     -1, -2, -3, -4, -5, -6, -7, -8)
@@ -50,6 +51,22 @@ class SrwmBwdArgs(C.Structure):
                 ("grad_W_y", State), ("grad_W_q", State), ("grad_W_k", State), ("grad_w_b", State)]
 
 
+class SrwmExt(C.Structure):
+    _fields_ = [("base_W_y", State), ("base_W_q", State), ("base_W_k", State), ("base_w_b", State),
+                ("shift_W_y", State), ("shift_W_q", State), ("shift_W_k", State), ("shift_w_b", State),
+                ("done", C.c_void_p), ("done_stride_n", C.c_int64), ("done_stride_l", C.c_int64)]
+
+
+class SrwmBwdDetArgs(C.Structure):
+    _fields_ = [("N", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("E", C.c_int32),
+                ("io_dtype", C.c_int32), ("flags", C.c_uint32), ("variant", C.c_int32),
+                ("reserved", C.c_int32),
+                ("x", Seq), ("k", Seq), ("beta", Seq), ("y_diff", Seq), ("grad_out", Seq),
+                ("base_W_y", State), ("shift_W_y", State),
+                ("done", C.c_void_p), ("done_stride_n", C.c_int64), ("done_stride_l", C.c_int64),
+                ("grad_x", Seq), ("grad_W_y", State)]
+
+
 class DeltaFwdArgs(C.Structure):
     _fields_ = [("N", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("E", C.c_int32),
                 ("M", C.c_int32), ("io_dtype", C.c_int32), ("flags", C.c_uint32),
@@ -72,6 +89,9 @@ class DeltaBwdArgs(C.Structure):
 SYMBOLS = {
     "srwm_b200_srwm_forward": (C.c_int, [C.POINTER(SrwmFwdArgs), C.c_void_p]),
     "srwm_b200_srwm_backward": (C.c_int, [C.POINTER(SrwmBwdArgs), C.c_void_p]),
+    "srwm_b200_srwm_layer_forward": (C.c_int, [C.POINTER(SrwmFwdArgs), C.POINTER(SrwmExt), C.c_void_p]),
+    "srwm_b200_srwm_layer_backward": (C.c_int, [C.POINTER(SrwmBwdArgs), C.POINTER(SrwmExt), C.c_void_p]),
+    "srwm_b200_srwm_backward_detached": (C.c_int, [C.POINTER(SrwmBwdDetArgs), C.c_void_p]),
     "srwm_b200_delta_forward": (C.c_int, [C.POINTER(DeltaFwdArgs), C.c_void_p]),
     "srwm_b200_delta_backward": (C.c_int, [C.POINTER(DeltaBwdArgs), C.c_void_p]),
     "srwm_b200_reduce_batch": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_void_p,
@@ -104,7 +124,7 @@ def load():
             continue        # optional symbols are checked by their users
         fn.restype = res
         fn.argtypes = args
-    if lib.srwm_b200_abi_version() != 1:
+    if lib.srwm_b200_abi_version() != ABI_VERSION:
         raise RuntimeError("libsrwm_b200.so ABI version mismatch")
     _lib = lib
     return lib

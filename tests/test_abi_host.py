@@ -27,7 +27,8 @@ def test_library_exports_every_declared_symbol():
     for name in declared:
         assert hasattr(lib, name), f"{name} declared in the header but not exported"
         assert name in L.SYMBOLS, f"{name} has no ctypes prototype"
-    assert lib.srwm_b200_abi_version() == 1
+    assert lib.srwm_b200_abi_version() == L.ABI_VERSION == int(
+        re.search(r"#define SRWM_B200_ABI_VERSION (\d+)", _header()).group(1))
 
 
 def test_ctypes_structs_match_the_header_layout():
@@ -42,6 +43,8 @@ int main(void) {
          sizeof(srwm_b200_delta_fwd_args), sizeof(srwm_b200_delta_bwd_args));
   printf("%zu %zu %zu %zu\n", offsetof(srwm_b200_srwm_fwd_args, out), offsetof(srwm_b200_srwm_bwd_args, grad_x),
          offsetof(srwm_b200_delta_fwd_args, W), offsetof(srwm_b200_delta_bwd_args, grad_W0));
+  printf("%zu %zu %zu %zu\n", sizeof(srwm_b200_srwm_ext), offsetof(srwm_b200_srwm_ext, done),
+         sizeof(srwm_b200_srwm_bwd_detached_args), offsetof(srwm_b200_srwm_bwd_detached_args, grad_x));
   return 0;
 }'''
     with tempfile.TemporaryDirectory() as td:
@@ -54,14 +57,16 @@ int main(void) {
     sizes = [int(v) for v in out]
     assert sizes[:6] == [C.sizeof(L.Seq), C.sizeof(L.State), C.sizeof(L.SrwmFwdArgs), C.sizeof(L.SrwmBwdArgs),
                          C.sizeof(L.DeltaFwdArgs), C.sizeof(L.DeltaBwdArgs)]
-    assert sizes[6:] == [L.SrwmFwdArgs.out.offset, L.SrwmBwdArgs.grad_x.offset, L.DeltaFwdArgs.W.offset,
-                         L.DeltaBwdArgs.grad_W0.offset]
+    assert sizes[6:10] == [L.SrwmFwdArgs.out.offset, L.SrwmBwdArgs.grad_x.offset, L.DeltaFwdArgs.W.offset,
+                           L.DeltaBwdArgs.grad_W0.offset]
+    assert sizes[10:] == [C.sizeof(L.SrwmExt), L.SrwmExt.done.offset, C.sizeof(L.SrwmBwdDetArgs),
+                          L.SrwmBwdDetArgs.grad_x.offset]
 
 
 def test_queries():
     lib = L.load()
     assert [lib.srwm_b200_head_dim_supported(e) for e in (8, 16, 32, 64, 12, 128)] == [1, 1, 1, 1, 0, 0]
-    for op in range(4):
+    for op in range(5):
         for E in (8, 16, 32, 64):
             assert lib.srwm_b200_num_variants(op, E) >= 1
             info = L.describe(op, E, L.BF16, 0)
@@ -111,6 +116,41 @@ def test_invalid_calls_are_rejected_before_any_cuda_call():
     assert lib.srwm_b200_delta_backward(C.byref(db), None) == L.ERR_NULL
     assert lib.srwm_b200_reduce_batch(None, 4, -1, 4, None, 0, None) == L.ERR_SHAPE
     assert lib.srwm_b200_reduce_batch(None, 4, 1, 4, None, 0, None) == L.ERR_NULL
+
+
+def test_layer_level_calls_validate_their_extension_block():
+    lib = L.load()
+    f = lib.srwm_b200_srwm_layer_forward
+    st, sb = L.State(0x2000, 0, 256), L.State(0x2000, 0, 64)
+
+    def ext(**kw):
+        e = L.SrwmExt()
+        e.base_W_y = e.base_W_q = e.base_W_k = st
+        e.base_w_b = sb
+        for k, v in kw.items():
+            setattr(e, k, v)
+        return e
+
+    none = L.State(None, 0, 0)
+    assert f(C.byref(_fwd_args(N=0)), C.byref(ext()), None) == 0
+    assert f(C.byref(_fwd_args()), C.byref(ext(base_W_q=none)), None) == L.ERR_NULL           # all four or none
+    assert f(C.byref(_fwd_args()), C.byref(ext(shift_W_y=st)), None) == L.ERR_NULL            # all four or none
+    assert f(C.byref(_fwd_args()), C.byref(ext(base_W_k=L.State(0x2004, 0, 256))), None) == L.ERR_ALIGN
+    e = L.SrwmExt()                                                                           # no base at all ...
+    e.done = 0x3000
+    assert f(C.byref(_fwd_args()), C.byref(e), None) == L.ERR_NULL                            # ... but a reset mask
+    b = L.SrwmBwdArgs()
+    b.N, b.H, b.L, b.E = 1, 1, 1, 16
+    assert lib.srwm_b200_srwm_layer_backward(C.byref(b), C.byref(ext()), None) == L.ERR_NULL
+    dargs = L.SrwmBwdDetArgs()
+    dargs.N, dargs.H, dargs.L, dargs.E = 1, 1, 1, 16
+    g = lib.srwm_b200_srwm_backward_detached
+    assert g(None, None) == L.ERR_NULL
+    assert g(C.byref(dargs), None) == L.ERR_NULL
+    dargs.E = 24
+    assert g(C.byref(dargs), None) == L.ERR_HEAD_DIM
+    dargs.E, dargs.N = 16, 0
+    assert g(C.byref(dargs), None) == 0
 
 
 def test_operators_refuse_cpu_tensors():

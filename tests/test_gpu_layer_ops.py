@@ -1,0 +1,223 @@
+"""GPU parity tests of the layer-level SRWM calls (input softmax, un-repeated slow weights with
+the state carried as a shift, in-kernel episode resets, detached-state backward) against the
+CPU oracle of the reference layers' code around the operator (oracle/srwm_layer_oracle.py).
+
+Tolerances as for the plain operator: forward <= 1e-4, gradients <= 1e-3 (whole-tensor max
+error over max magnitude, fp32 activations); bf16 activations carry their own rounding.
+"""
+import pytest
+import torch
+
+import srwm_layer_oracle as lorc
+import srwm_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+FWD_TOL, GRAD_TOL = 1e-4, 1e-3
+BF16_TOL = 8e-3
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _layer_inputs(N, H, L, E, seed, with_shift=True):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(N, H, L, E, generator=g)
+    std = E ** -0.5
+    base = [torch.randn(1, H, E, E, generator=g) * std for _ in range(3)]
+    base.append(torch.randn(1, H, E, 4, generator=g) * std)
+    shift = None
+    if with_shift:
+        shift = [torch.randn(N, H, E, E, generator=g) * 0.1 * std for _ in range(3)]
+        shift.append(torch.randn(N, H, E, 4, generator=g) * 0.1 * std)
+    go = torch.randn(N, H, L, E, generator=g)
+    gs = [torch.randn(N, H, E, E, generator=g) for _ in range(3)] + [torch.randn(N, H, E, 4, generator=g)]
+    return x, base, shift, go, gs
+
+
+def _leaf(ts, dtype=torch.float64, device="cpu"):
+    return [t.to(device=device, dtype=dtype).requires_grad_() for t in ts]
+
+
+@pytest.mark.parametrize("E", [8, 16, 32, 64])
+@pytest.mark.parametrize("with_shift", [False, True])
+@pytest.mark.parametrize("input_softmax", [False, True])
+def test_layer_bptt_parity(E, with_shift, input_softmax):
+    from srwm_b200.layer_ops import srwm_layer
+    N, H, L = 3, 2, 21
+    x, base, shift, go, gs = _layer_inputs(N, H, L, E, 100 + E, with_shift)
+    # oracle (fp64, autograd); the loss also reads the returned shift so that gradient flows into it
+    xo = x.double().requires_grad_()
+    bo = _leaf(base)
+    so = _leaf(shift) if with_shift else None
+    out_o, sh_o = lorc.srwm_layer(xo, bo, so, input_softmax)
+    loss = (out_o * go.double()).sum() + sum((s * g.double()).sum() for s, g in zip(sh_o, gs))
+    loss.backward()
+    # kernels
+    d = _dev()
+    xd = x.to(d).requires_grad_()
+    bd = _leaf(base, torch.float32, d)
+    sd = _leaf(shift, torch.float32, d) if with_shift else None
+    out, sh = srwm_layer(xd, *bd, shift=sd, input_softmax=input_softmax)
+    assert orc.rel_max(out.detach().cpu(), out_o.detach()) < FWD_TOL
+    for a, b in zip(sh, sh_o):
+        assert a.shape == b.shape
+        # the shift is a difference of two states: hold it to the tolerance at the states' scale
+        assert float((a.detach().cpu() - b.detach()).abs().max()) < FWD_TOL * E ** -0.5
+    loss_d = (out * go.to(d)).sum() + sum((s * g.to(d)).sum() for s, g in zip(sh, gs))
+    loss_d.backward()
+    assert orc.rel_max(xd.grad.cpu(), xo.grad) < GRAD_TOL
+    for a, b in zip(bd, bo):
+        assert a.grad.shape == b.grad.shape
+        assert orc.rel_max(a.grad.cpu(), b.grad) < GRAD_TOL
+    if with_shift:
+        for a, b in zip(sd, so):
+            assert orc.rel_max(a.grad.cpu(), b.grad) < GRAD_TOL
+
+
+@pytest.mark.parametrize("E", [8, 16, 32, 64])
+@pytest.mark.parametrize("input_softmax", [False, True])
+def test_layer_unroll_detached_with_resets(E, input_softmax):
+    from srwm_b200.layer_ops import srwm_layer
+    N, H, T = 4, 2, 37
+    x, base, shift, go, _ = _layer_inputs(N, H, T, E, 200 + E, True)
+    g = torch.Generator().manual_seed(7)
+    done = torch.rand(N, T, generator=g) < 0.12
+    done[0, 0] = True            # a reset before the very first step
+    done[1] = False              # a sample without any reset
+    done[2, T - 1] = True        # and one at the last step
+    xo = x.double().requires_grad_()
+    bo = _leaf(base)
+    out_o, sh_o = lorc.srwm_unroll_detached(xo, bo, [s.double() for s in shift], done, input_softmax)
+    (out_o * go.double()).sum().backward()
+
+    d = _dev()
+    xd = x.to(d).requires_grad_()
+    bd = _leaf(base, torch.float32, d)
+    sd = [s.to(d) for s in shift]
+    # the learner's mask is [T, B]: hand it in as the transposed view
+    done_tb = done.t().contiguous().to(d)
+    out, sh = srwm_layer(xd, *bd, shift=sd, done=done_tb.t(), input_softmax=input_softmax, detach_state=True)
+    assert orc.rel_max(out.detach().cpu(), out_o.detach()) < FWD_TOL
+    for a, b in zip(sh, sh_o):
+        assert not a.requires_grad
+        assert float((a.cpu() - b).abs().max()) < FWD_TOL * E ** -0.5
+    (out * go.to(d)).sum().backward()
+    assert orc.rel_max(xd.grad.cpu(), xo.grad) < GRAD_TOL
+    assert orc.rel_max(bd[0].grad.cpu(), bo[0].grad) < GRAD_TOL
+    for a, b in zip(bd[1:], bo[1:]):   # the detached state passes nothing to W_q, W_k, w_b
+        assert float(a.grad.abs().max()) == 0.0
+        assert b.grad is None or float(b.grad.abs().max()) == 0.0
+
+
+def test_layer_detached_equals_one_step_calls_of_the_plain_operator():
+    """The fused unroll against T one-step calls of the drop-in operator, composed as the
+    reference layer composes them (torchbeast/layer.py:378-421), all on the GPU."""
+    import srwm_b200 as sb
+    from srwm_b200.layer_ops import srwm_layer
+    N, H, T, E = 5, 4, 12, 32
+    x, base, shift, go, _ = _layer_inputs(N, H, T, E, 321, True)
+    d = _dev()
+    done = (torch.rand(N, T, generator=torch.Generator().manual_seed(3)) < 0.2).to(d)
+    xd = x.to(d).requires_grad_()
+    bd = _leaf(base, torch.float32, d)
+    out, sh = srwm_layer(xd, *bd, shift=[s.to(d) for s in shift], done=done, detach_state=True)
+    (out * go.to(d)).sum().backward()
+
+    x2 = x.to(d).requires_grad_()
+    b2 = _leaf(base, torch.float32, d)
+    st = [s.to(d) for s in shift]
+    outs = []
+    for t in range(T):
+        nd = (~done[:, t]).float().view(N, 1, 1, 1)
+        st = [nd * s for s in st]
+        W = [s + b.repeat(N, 1, 1, 1) for s, b in zip(st, b2)]
+        o = sb.self_ref_v0(torch.softmax(x2[:, :, t:t + 1], -1), *W)
+        st = [w.detach() - b.detach().repeat(N, 1, 1, 1) for w, b in zip(W, b2)]
+        outs.append(o)
+    out2 = torch.cat(outs, 2)
+    (out2 * go.to(d)).sum().backward()
+    assert orc.rel_max(out.detach(), out2.detach()) < FWD_TOL
+    assert orc.rel_max(xd.grad, x2.grad) < GRAD_TOL
+    assert orc.rel_max(bd[0].grad, b2[0].grad) < GRAD_TOL
+    for a, b in zip(sh, st):
+        assert float((a - b).abs().max()) < FWD_TOL * E ** -0.5
+
+
+@pytest.mark.parametrize("E", [16, 64])
+def test_layer_style_views_bf16(E):
+    """[L, B, H*d] bf16 activations handed in as the permuted view the layers build; the output
+    comes back in the same memory order, so the layers' reshape stays a view."""
+    from srwm_b200.layer_ops import srwm_layer
+    B, H, L = 4, 2, 33
+    g = torch.Generator().manual_seed(5)
+    h = torch.randn(L, B, H * E, generator=g).bfloat16()
+    _, base, shift, _, _ = _layer_inputs(B, H, L, E, 55, True)
+    go = torch.randn(L, B, H * E, generator=g).bfloat16()
+    xo = h.double().view(L, B, H, E).permute(1, 2, 0, 3).requires_grad_()
+    bo = _leaf(base)
+    out_o, sh_o = lorc.srwm_layer(xo, bo, [s.double() for s in shift], True)
+    (out_o * go.double().view(L, B, H, E).permute(1, 2, 0, 3)).sum().backward()
+
+    d = _dev()
+    hd = h.to(d).requires_grad_()
+    bd = _leaf(base, torch.float32, d)
+    x = hd.view(L, B, H, E).permute(1, 2, 0, 3)
+    out, sh = srwm_layer(x, *bd, shift=[s.to(d) for s in shift])
+    res = out.transpose(1, 2).reshape(B, L, H * E).transpose(0, 1)     # layer.py:184-186
+    assert res.data_ptr() == out.data_ptr() and res.is_contiguous()
+    assert orc.rel_max(out.detach().float().cpu(), out_o.detach()) < BF16_TOL
+    (res * go.to(d)).sum().backward()
+    assert orc.rel_max(hd.grad.float().cpu().view(L, B, H, E).permute(1, 2, 0, 3), xo.grad) < BF16_TOL
+    for a, b in zip(bd, bo):
+        assert orc.rel_max(a.grad.cpu(), b.grad) < GRAD_TOL
+    for a, b in zip(sh, sh_o):
+        assert float((a.detach().cpu() - b.detach()).abs().max()) < FWD_TOL * E ** -0.5
+
+
+def test_layer_per_sample_base_and_plain_entry_flag():
+    """Slow weights given per sample ([N,H,E,.]) get per-sample gradients; the input-softmax
+    flag alone (no base) goes through the plain entry points."""
+    from srwm_b200 import _lib as L
+    from srwm_b200 import ops
+    from srwm_b200.layer_ops import srwm_layer
+    N, H, Ln, E = 2, 3, 19, 16
+    x, base, _, go, _ = _layer_inputs(N, H, Ln, E, 77, False)
+    base = [b.repeat(N, 1, 1, 1) + 0.01 * torch.randn(N, *b.shape[1:]) for b in base]
+    xo = x.double().requires_grad_()
+    bo = _leaf(base)
+    out_o, WL = orc.srwm_loop(torch.softmax(xo, -1), *bo)
+    (out_o * go.double()).sum().backward()
+    d = _dev()
+    xd = x.to(d).requires_grad_()
+    bd = _leaf(base, torch.float32, d)
+    out, sh = srwm_layer(xd, *bd)
+    (out * go.to(d)).sum().backward()
+    assert orc.rel_max(out.detach().cpu(), out_o.detach()) < FWD_TOL
+    assert orc.rel_max(xd.grad.cpu(), xo.grad) < GRAD_TOL
+    for a, b in zip(bd, bo):
+        assert a.grad.shape == b.grad.shape and orc.rel_max(a.grad.cpu(), b.grad) < GRAD_TOL
+    # plain entry point with the flag: state in, final state out, as the reference operator
+    import ctypes as C
+    Wd = [b.to(d).clone() for b in base]
+    xs = x.to(d)
+    outp = torch.empty_like(xs)
+    a = L.SrwmFwdArgs()
+    a.N, a.H, a.L, a.E = N, H, Ln, E
+    a.io_dtype = L.F32
+    a.flags = L.FLAG_NO_SAVE | L.FLAG_INPUT_SOFTMAX
+    a.x, a.out = ops._seq_desc(xs), ops._seq_desc(outp)
+    a.W_y, a.W_q, a.W_k, a.w_b = (ops._state_desc(t) for t in Wd)
+    L.check(L.load().srwm_b200_srwm_forward(C.byref(a), ops._stream(xs)), "srwm_forward")
+    assert orc.rel_max(outp.cpu(), out_o.detach()) < FWD_TOL
+    for t, o in zip(Wd, WL):
+        assert orc.rel_max(t.cpu(), o.detach()) < FWD_TOL
+
+
+def test_layer_done_needs_detached_state():
+    from srwm_b200.layer_ops import srwm_layer
+    d = _dev()
+    x, base, _, _, _ = _layer_inputs(2, 2, 5, 8, 1, False)
+    with pytest.raises(ValueError):
+        srwm_layer(x.to(d), *[b.to(d) for b in base], done=torch.zeros(2, 5, dtype=torch.bool, device=d))
