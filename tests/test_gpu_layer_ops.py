@@ -221,3 +221,114 @@ def test_layer_done_needs_detached_state():
     x, base, _, _, _ = _layer_inputs(2, 2, 5, 8, 1, False)
     with pytest.raises(ValueError):
         srwm_layer(x.to(d), *[b.to(d) for b in base], done=torch.zeros(2, 5, dtype=torch.bool, device=d))
+
+
+# ---------------------------------------------------------------------------------------
+# the two layers against the reference layers' composition around the drop-in operator
+# ---------------------------------------------------------------------------------------
+
+def _composed_layer(layer, h, state, get_state, stateful, always_softmax=False):
+    """What the reference layers compute (supervised_learning/layer.py:156-209,
+    reinforcement_learning/torchbeast/layer.py:378-421), written with torch ops around the
+    drop-in operator."""
+    import srwm_b200 as sb
+    slen, bsz, _ = h.shape
+    H, E = layer.num_head, layer.dim_head
+    x = h.reshape(slen, bsz, H, E)
+    if always_softmax or layer.use_input_softmax:
+        x = torch.softmax(x, dim=-1)
+    x = x.permute(1, 2, 0, 3)
+    Ws = [w.repeat(bsz, 1, 1, 1) for w in (layer.W_y, layer.W_q, layer.W_k, layer.w_b)]
+    if state is not None:
+        Ws = [s + w for s, w in zip(state, Ws)]
+    if stateful:
+        out, *Ws = sb.stateful_self_ref_v0(x, *Ws)
+    else:
+        out = sb.self_ref_v0(x, *Ws)
+    out = out.transpose(1, 2).reshape(bsz, slen, H * E).transpose(0, 1)
+    out = layer.drop(layer.out_linear(out))
+    res = (layer.layer_norm(h) if getattr(layer, "use_ln", False) else h) + out
+    if get_state:
+        new = tuple(w - b.repeat(bsz, 1, 1, 1) for w, b in zip(Ws, (layer.W_y, layer.W_q, layer.W_k, layer.w_b)))
+        return res, new
+    return res
+
+
+@pytest.mark.parametrize("use_ln,use_softmax,stateful", [(True, False, False), (False, True, True), (True, True, True)])
+def test_srwm_layer_module_matches_composition(use_ln, use_softmax, stateful):
+    from srwm_b200.layers import SRWMlayer
+    d = _dev()
+    torch.manual_seed(0)
+    H, E, D, L, B = 4, 16, 64, 24, 3
+    layer = SRWMlayer(H, E, D, 0.0, use_ln=use_ln, use_input_softmax=use_softmax, stateful=stateful).to(d)
+    h = torch.randn(L, B, D, device=d)
+    tgt = torch.randn(L, B, D, device=d)
+    gs = [torch.randn(B, H, E, E, device=d) for _ in range(3)] + [torch.randn(B, H, E, 4, device=d)]
+    st0 = [0.05 * torch.randn_like(g) for g in gs]
+
+    def run(fused):
+        layer.zero_grad()
+        hh = h.clone().requires_grad_()
+        st = [s.clone().requires_grad_() for s in st0]
+        if fused:
+            out, new = layer(hh, state=st, get_state=True)
+        else:
+            out, new = _composed_layer(layer, hh, st, True, stateful)
+        loss = (out * tgt).sum()
+        if stateful:
+            loss = loss + sum((n * g).sum() for n, g in zip(new, gs))
+        loss.backward()
+        grads = [p.grad.clone() for p in layer.parameters()]
+        return out.detach(), [n.detach() for n in new], hh.grad, [s.grad for s in st], grads
+
+    o1, n1, gh1, gst1, gp1 = run(True)
+    o2, n2, gh2, gst2, gp2 = run(False)
+    assert orc.rel_max(o1, o2) < FWD_TOL
+    for a, b in zip(n1, n2):
+        assert float((a - b).abs().max()) < FWD_TOL * E ** -0.5
+    assert orc.rel_max(gh1, gh2) < GRAD_TOL
+    for a, b in zip(gst1, gst2):
+        assert orc.rel_max(a, b) < GRAD_TOL
+    for a, b, (name, _) in zip(gp1, gp2, layer.named_parameters()):
+        assert orc.rel_max(a, b) < GRAD_TOL, name
+
+
+def test_sr_layer_unroll_matches_the_learner_loop():
+    from srwm_b200.layers import SRlayer
+    d = _dev()
+    torch.manual_seed(1)
+    H, E, D, T, B = 8, 32, 256, 20, 6
+    layer = SRlayer(H, E, D, 0.0).to(d)
+    h = torch.randn(T, B, D, device=d)
+    tgt = torch.randn(T, B, D, device=d)
+    done = torch.rand(T, B, device=d) < 0.15
+    st0 = [0.05 * torch.randn(B, H, E, E, device=d) for _ in range(3)] + [0.05 * torch.randn(B, H, E, 4, device=d)]
+
+    layer.zero_grad()
+    h1 = h.clone().requires_grad_()
+    out1, s1 = layer.unroll(h1, done, [s.clone() for s in st0])
+    (out1 * tgt).sum().backward()
+    g1 = {n: p.grad.clone() for n, p in layer.named_parameters() if p.grad is not None}
+
+    # reinforcement_learning/torchbeast_procgen/model.py:1180-1197 around the layer's own forward
+    layer.zero_grad()
+    h2 = h.clone().requires_grad_()
+    st = [s.clone() for s in st0]
+    outs = []
+    for t in range(T):
+        nd = (~done[t]).float().view(B, 1, 1, 1)
+        st = [nd * s for s in st]
+        o, st = _composed_layer(layer, h2[t:t + 1], st, True, False, always_softmax=True)
+        st = [s.detach() for s in st]
+        outs.append(o)
+    out2 = torch.cat(outs, 0)
+    (out2 * tgt).sum().backward()
+    assert orc.rel_max(out1.detach(), out2.detach()) < FWD_TOL
+    assert orc.rel_max(h1.grad, h2.grad) < GRAD_TOL
+    for a, b in zip(s1, st):
+        assert float((a - b).abs().max()) < FWD_TOL * E ** -0.5
+    for n, p in layer.named_parameters():
+        if n in ("W_q", "W_k", "w_b"):
+            assert float(g1[n].abs().max()) == 0.0 and float(p.grad.abs().max()) < 1e-6
+        elif p.grad is not None:
+            assert orc.rel_max(g1[n], p.grad) < GRAD_TOL, n
