@@ -558,6 +558,114 @@ def run_table(args):
           flush=True)
 
 
+def composed_sr_layer(layer, h, state, always_softmax=True):
+    """What the reference layers do around the operator (reinforcement_learning/torchbeast/
+    layer.py:378-421, supervised_learning/layer.py:156-209), written with torch ops around the
+    drop-in ``self_ref_v0`` -- the unfused arm of the layer-level timings."""
+    import srwm_b200 as sb
+    slen, bsz, _ = h.shape
+    H, E = layer.num_head, layer.dim_head
+    x = h.reshape(slen, bsz, H, E)
+    if always_softmax or getattr(layer, "use_input_softmax", False):
+        x = torch.softmax(x, dim=-1)
+    x = x.permute(1, 2, 0, 3)
+    base = (layer.W_y, layer.W_q, layer.W_k, layer.w_b)
+    Ws = [w.repeat(bsz, 1, 1, 1) for w in base]
+    if state is not None:
+        Ws = [s + w for s, w in zip(state, Ws)]
+    out = sb.self_ref_v0(x, *Ws)
+    out = out.transpose(1, 2).reshape(bsz, slen, H * E).transpose(0, 1)
+    out = layer.drop(layer.out_linear(out))
+    out = (layer.layer_norm(h) if getattr(layer, "use_ln", False) else h) + out
+    new = tuple(w.detach() - b.detach().repeat(bsz, 1, 1, 1) for w, b in zip(Ws, base))
+    return out, new
+
+
+def run_layer_table(args):
+    """Layer-level timings: the fused layer call against the same layer composed from torch
+    ops around the drop-in operator (both use this library's kernels for the recurrence)."""
+    from srwm_b200.layers import SRWMlayer, SRlayer
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    torch.manual_seed(0)
+
+    def emit(name, cfg, fused, composed, extra=None):
+        ms_f = timed_region(fused, args.steps, args.warmup, False, device)
+        ms_c = timed_region(composed, args.steps, args.warmup, False, device)
+        line = {"workload": name, "config": cfg, "fused_ms": ms_f, "composed_ms": ms_c, "speedup": ms_c / ms_f}
+        line.update(extra or {})
+        print(json.dumps(line), flush=True)
+
+    # supervised-learning layer, the few-shot model's size: B=128 L=128 H=16 d=32 (dim 512)
+    L_, B, H, E = 128, 128, 16, 32
+    layer = SRWMlayer(H, E, H * E, 0.0, use_ln=True, use_input_softmax=True).to(device)
+    h = torch.randn(L_, B, H * E, device=device)
+    tgt = torch.randn(L_, B, H * E, device=device)
+
+    def sl_fused(_t):
+        layer.zero_grad(set_to_none=True)
+        hh = h.clone().requires_grad_()
+        (layer(hh) * tgt).sum().backward()
+
+    def sl_composed(_t):
+        layer.zero_grad(set_to_none=True)
+        hh = h.clone().requires_grad_()
+        (composed_sr_layer(layer, hh, None, always_softmax=False)[0] * tgt).sum().backward()
+
+    emit("srwm_c3_layer", "SRWMlayer fwd+bwd, L=128 B=128 H=16 d=32 dim=512, input softmax, layer norm, fp32",
+         sl_fused, sl_composed, {"tokens": L_ * B})
+
+    # reinforcement-learning learner unroll: T=100 B=32 H=8 d=32 (hidden 256), done mask, detached state
+    T, B, H, E = 100, 32, 8, 32
+    rl = SRlayer(H, E, H * E, 0.0).to(device)
+    h = torch.randn(T, B, H * E, device=device)
+    tgt = torch.randn(T, B, H * E, device=device)
+    done = torch.rand(T, B, device=device) < 0.01
+    st0 = [0.05 * torch.randn(B, H, E, E, device=device) for _ in range(3)] + [0.05 * torch.randn(B, H, E, 4, device=device)]
+
+    def rl_fused(_t):
+        rl.zero_grad(set_to_none=True)
+        hh = h.clone().requires_grad_()
+        out, _ = rl.unroll(hh, done, st0)
+        (out * tgt).sum().backward()
+
+    def rl_composed(_t):
+        rl.zero_grad(set_to_none=True)
+        hh = h.clone().requires_grad_()
+        st = st0
+        outs = []
+        for t in range(T):     # reinforcement_learning/torchbeast_procgen/model.py:1180-1197
+            nd = (~done[t]).float().view(B, 1, 1, 1)
+            st = [nd * s for s in st]
+            o, st = composed_sr_layer(rl, hh[t:t + 1], st)
+            outs.append(o)
+        (torch.cat(outs, 0) * tgt).sum().backward()
+
+    emit("srwm_c4_learner_unroll", "SRlayer learner unroll fwd+bwd, T=100 B=32 H=8 d=32 hidden=256, done mask, "
+         "state detached per step: one fused call vs 100 one-step layer calls", rl_fused, rl_composed,
+         {"env_steps": T * B})
+
+    # actor: one step, B=48, state carried, no_grad, 100 consecutive calls
+    B = 48
+    ha = torch.randn(1, B, H * E, device=device)
+    sta = [0.05 * torch.randn(B, H, E, E, device=device) for _ in range(3)] + [0.05 * torch.randn(B, H, E, 4, device=device)]
+
+    def actor_fused(_t):
+        st = sta
+        with torch.no_grad():
+            for _ in range(100):
+                _, st = rl(ha, st)
+
+    def actor_composed(_t):
+        st = sta
+        with torch.no_grad():
+            for _ in range(100):
+                _, st = composed_sr_layer(rl, ha, st)
+
+    emit("srwm_c4_actor_layer", "SRlayer forward, L=1 B=48 H=8 d=32 hidden=256, state carried, no_grad, "
+         "100 consecutive layer calls per step", actor_fused, actor_composed, {"calls": 100})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -570,8 +678,12 @@ def main():
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--table", action="store_true", help="operator-level timings of every configuration")
+    ap.add_argument("--layer-table", action="store_true",
+                    help="layer-level timings: fused layer call vs torch ops around the operator")
     args = ap.parse_args()
-    if args.table:
+    if args.layer_table:
+        run_layer_table(args)
+    elif args.table:
         run_table(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -351,27 +351,48 @@ int srwm_b200_delta_backward(const srwm_b200_delta_bwd_args* a, void* stream) {
 }  // extern "C"
 
 // ---------------------------------------------------------------------------------------
-// Batch reduction: dst[i] (+)= sum_n src[n*stride_n + i].  One thread per 4 outputs, the
-// batch walked in a fixed order (deterministic); reads are 16-byte and coalesced.
+// Batch reduction: dst[i] (+)= sum_n src[n*stride_n + i].  A block of 1024 threads covers 128
+// outputs (32 lanes x float4) and splits the batch over its 32 warps (four independent loads
+// in flight per thread); the 32 partial sums are combined through shared memory in a fixed
+// order, so the result does not depend on timing.  Reads are 16-byte and coalesced.
 // ---------------------------------------------------------------------------------------
 namespace {
-__global__ void __launch_bounds__(256) reduce_batch_kernel(const float* __restrict__ src, long long stride_n, int N,
-                                                           long long count, float* __restrict__ dst, int accumulate) {
-  const long long i4 = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long i = i4 * 4;
-  if (i >= count) return;
-  if (i + 4 <= count) {
-    float4 acc = accumulate ? *reinterpret_cast<const float4*>(dst + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-    for (int n = 0; n < N; ++n) {
-      const float4 v = *reinterpret_cast<const float4*>(src + (long long)n * stride_n + i);
-      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+constexpr int RB_SLICES = 32;
+__device__ __forceinline__ void add4(float4& a, const float4& v) { a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w; }
+
+__global__ void __launch_bounds__(32 * RB_SLICES) reduce_batch_kernel(const float* __restrict__ src, long long stride_n,
+                                                                      int N, long long count, float* __restrict__ dst,
+                                                                      int accumulate) {
+  __shared__ float4 part[RB_SLICES][32];
+  const int lane = threadIdx.x % 32, slice = threadIdx.x / 32;
+  const long long i = ((long long)blockIdx.x * 32 + lane) * 4;
+  const bool full = i + 4 <= count;
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (full) {
+    const float* s0 = src + i;
+    int n = slice;
+    for (; n + 3 * RB_SLICES < N; n += 4 * RB_SLICES) {
+      const float4 v0 = *reinterpret_cast<const float4*>(s0 + (long long)n * stride_n);
+      const float4 v1 = *reinterpret_cast<const float4*>(s0 + (long long)(n + RB_SLICES) * stride_n);
+      const float4 v2 = *reinterpret_cast<const float4*>(s0 + (long long)(n + 2 * RB_SLICES) * stride_n);
+      const float4 v3 = *reinterpret_cast<const float4*>(s0 + (long long)(n + 3 * RB_SLICES) * stride_n);
+      add4(acc, v0); add4(acc, v1); add4(acc, v2); add4(acc, v3);
     }
-    *reinterpret_cast<float4*>(dst + i) = acc;
-  } else {
+    for (; n < N; n += RB_SLICES) add4(acc, *reinterpret_cast<const float4*>(s0 + (long long)n * stride_n));
+  }
+  part[slice][lane] = acc;
+  __syncthreads();
+  if (slice != 0 || i >= count) return;
+  if (full) {
+    float4 t = accumulate ? *reinterpret_cast<const float4*>(dst + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int s8 = 0; s8 < RB_SLICES; ++s8) add4(t, part[s8][lane]);
+    *reinterpret_cast<float4*>(dst + i) = t;
+  } else {   // ragged end: fewer than four outputs left
     for (long long j = i; j < count; ++j) {
-      float acc = accumulate ? dst[j] : 0.f;
-      for (int n = 0; n < N; ++n) acc += src[(long long)n * stride_n + j];
-      dst[j] = acc;
+      float t = accumulate ? dst[j] : 0.f;
+      for (int n = 0; n < N; ++n) t += src[(long long)n * stride_n + j];
+      dst[j] = t;
     }
   }
 }
@@ -383,10 +404,9 @@ extern "C" int srwm_b200_reduce_batch(const float* src, int64_t stride_n, int32_
   if (count == 0) return 0;
   if (!dst || (N > 0 && !src)) return SRWM_B200_ERR_NULL;
   if ((uintptr_t)src % 16 || (uintptr_t)dst % 16 || (stride_n * 4) % 16) return SRWM_B200_ERR_ALIGN;
-  const long long n4 = (count + 3) / 4;
-  const long long blocks = (n4 + 255) / 256;
+  const long long blocks = (count + 127) / 128;
   if (blocks > 0x7fffffffLL) return SRWM_B200_ERR_SHAPE;
-  reduce_batch_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(src, stride_n, N, count, dst, accumulate);
+  reduce_batch_kernel<<<(unsigned)blocks, 32 * RB_SLICES, 0, (cudaStream_t)stream>>>(src, stride_n, N, count, dst, accumulate);
   const cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     g_last_cuda_error = (int)e;

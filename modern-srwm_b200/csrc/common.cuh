@@ -352,64 +352,66 @@ __device__ __forceinline__ void convert_rows(const TIO* src, float* dst, int nt,
   }
 }
 
-// Row-wise softmax of nt staged rows: dst[t][:] = softmax(src[t][:]) in fp32, one warp per row.
-// dst may be the same memory as src when the streamed type is float (a lane rewrites exactly
-// what it read).
-template <typename TIO, int E, int P>
+// Row-wise softmax of nt (<= T) staged rows: dst[t][:] = softmax(src[t][:]) in fp32.  A row is
+// handled by E/4 adjacent lanes with 4 values each, so a warp works on 128/E rows at once, and
+// the rows a thread takes part in are independent chains the compiler can overlap.  dst may
+// be the same memory as src when the streamed type is float (a lane rewrites exactly what it
+// read).
+template <typename TIO, int E, int P, int T>
 __device__ __forceinline__ void softmax_rows(const TIO* src, float* dst, int nt, int tid) {
-  constexpr int VPT = E >= 32 ? E / 32 : 1;
-  const int warp = tid / 32, lane = tid % 32;
-  const bool active = lane * VPT < E;
-  for (int t = warp; t < nt; t += P / 32) {
-    float v[VPT];
-    if (active) {
-      ld_vec<VPT>(src + t * E + lane * VPT, v);
-    } else {
+  constexpr int LPR = E / 4;                 // lanes per row
+  constexpr int NG = P / LPR;                // rows in flight per pass over the block
+  constexpr int K = (T + NG - 1) / NG;       // passes
+  const int grp = tid / LPR, l = tid % LPR;
 #pragma unroll
-      for (int i = 0; i < VPT; ++i) v[i] = -INFINITY;
-    }
-    float m = v[0];
+  for (int kk = 0; kk < K; ++kk) {
+    const int t = grp + kk * NG;
+    const int tc = min(t, nt - 1);           // lanes past the end redo the last row and do not store
+    float v[4];
+    ld_vec<4>(src + tc * E + l * 4, v);
+    float m = fmaxf(fmaxf(v[0], v[1]), fmaxf(v[2], v[3]));
 #pragma unroll
-    for (int i = 1; i < VPT; ++i) m = fmaxf(m, v[i]);
-    m = warp_max(m);
-    float s = 0.f;
+    for (int off = 1; off < LPR; off <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, off));
+    float sum = 0.f;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) {
+    for (int i = 0; i < 4; ++i) {
       v[i] = __expf(v[i] - m);
-      s += v[i];
+      sum += v[i];
     }
-    s = allreduce_warp(s);
-    const float inv = __fdividef(1.f, s);
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) v[i] *= inv;
-    if (active) st_vec<VPT>(dst + t * E + lane * VPT, v);
+    for (int off = 1; off < LPR; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+    const float inv = __fdividef(1.f, sum);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) v[i] *= inv;
+    if (t < nt) st_vec<4>(dst + t * E + l * 4, v);
   }
 }
 
 // Backward of that softmax, applied to finished gradient rows on their way out:
 // out[t][e] = x[t][e] (g[t][e] - sum_e' g[t][e'] x[t][e']), rows of g `gstride` floats apart,
 // written as streamed type to global rows `row_stride_bytes` apart.
-template <typename TIO, int E, int P>
+template <typename TIO, int E, int P, int T>
 __device__ __forceinline__ void softmax_bwd_rows(const float* xs, const float* g, int gstride, char* grow0,
                                                  long long row_stride_bytes, int nt, int tid) {
-  constexpr int VPT = E >= 32 ? E / 32 : 1;
-  const int warp = tid / 32, lane = tid % 32;
-  const bool active = lane * VPT < E;
-  for (int t = warp; t < nt; t += P / 32) {
-    float xv[VPT], gv[VPT];
+  constexpr int LPR = E / 4;
+  constexpr int NG = P / LPR;
+  constexpr int K = (T + NG - 1) / NG;
+  const int grp = tid / LPR, l = tid % LPR;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) { xv[i] = 0.f; gv[i] = 0.f; }
-    if (active) {
-      ld_vec<VPT>(xs + t * E + lane * VPT, xv);
-      ld_vec<VPT>(g + (long long)t * gstride + lane * VPT, gv);
-    }
+  for (int kk = 0; kk < K; ++kk) {
+    const int t = grp + kk * NG;
+    const int tc = min(t, nt - 1);
+    float xv[4], gv[4];
+    ld_vec<4>(xs + tc * E + l * 4, xv);
+    ld_vec<4>(g + tc * gstride + l * 4, gv);
     float dot = 0.f;
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) dot = fmaf(xv[i], gv[i], dot);
-    dot = allreduce_warp(dot);
+    for (int i = 0; i < 4; ++i) dot = fmaf(xv[i], gv[i], dot);
 #pragma unroll
-    for (int i = 0; i < VPT; ++i) gv[i] = xv[i] * (gv[i] - dot);
-    if (active) st_vec<VPT>(reinterpret_cast<TIO*>(grow0 + t * row_stride_bytes) + lane * VPT, gv);
+    for (int off = 1; off < LPR; off <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) gv[i] = xv[i] * (gv[i] - dot);
+    if (t < nt) st_vec<4>(reinterpret_cast<TIO*>(grow0 + t * row_stride_bytes) + l * 4, gv);
   }
 }
 

@@ -208,7 +208,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
     if constexpr (EXT) {
       if (smx) {
         float* d = sizeof(TIO) == 4 ? reinterpret_cast<float*>(in_buf(c & 1)) : xf32;
-        softmax_rows<TIO, E, P>(sx, d, nt, tid);
+        softmax_rows<TIO, E, P, T>(sx, d, nt, tid);
         __syncthreads();
         sxs = d;
       }
@@ -526,12 +526,12 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
     if constexpr (sizeof(TIO) == 4) {
       float* xs = reinterpret_cast<float*>(in_buf(c & 1));
       if (smx) {
-        softmax_rows<TIO, E, P>(xs, xs, nt, tid);
+        softmax_rows<TIO, E, P, T>(xs, xs, nt, tid);
         __syncthreads();
       }
       sxf = xs;
     } else {
-      if (smx) softmax_rows<TIO, E, P>(in_buf(c & 1), xf32, nt, tid);
+      if (smx) softmax_rows<TIO, E, P, T>(in_buf(c & 1), xf32, nt, tid);
       else convert_rows<TIO, E, P>(in_buf(c & 1), xf32, nt, tid);
       __syncthreads();
       sxf = xf32;
@@ -850,11 +850,11 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
     if constexpr (EXT) {
       if constexpr (sizeof(TIO) == 4) {
         if (smx) {
-          softmax_rows<TIO, E, P>(sx, reinterpret_cast<float*>(ib), nt, tid);
+          softmax_rows<TIO, E, P, T>(sx, reinterpret_cast<float*>(ib), nt, tid);
           __syncthreads();
         }
       } else {
-        if (smx) softmax_rows<TIO, E, P>(sx, xf32, nt, tid);
+        if (smx) softmax_rows<TIO, E, P, T>(sx, xf32, nt, tid);
         else convert_rows<TIO, E, P>(sx, xf32, nt, tid);
         __syncthreads();
         sxs = xf32;
@@ -1174,7 +1174,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
     if constexpr (EXT) {
       if (smx) {
         __syncthreads();
-        softmax_bwd_rows<TIO, E, P>(sxs, sgx, NWARP * E, p.gx.row(n, h, t0), p.gx.sl, nt, tid);
+        softmax_bwd_rows<TIO, E, P, T>(sxs, sgx, NWARP * E, p.gx.row(n, h, t0), p.gx.sl, nt, tid);
         __syncthreads();   // softmax(x) may sit in the staging buffer the next prefetch overwrites
       }
     }
@@ -1298,11 +1298,11 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_det_kernel(const SrwmBwdDetP
     const float* sxs = reinterpret_cast<const float*>(ib);
     if constexpr (sizeof(TIO) == 4) {
       if (smx) {
-        softmax_rows<TIO, E, P>(sx, reinterpret_cast<float*>(ib), nt, tid);
+        softmax_rows<TIO, E, P, T>(sx, reinterpret_cast<float*>(ib), nt, tid);
         __syncthreads();
       }
     } else {
-      if (smx) softmax_rows<TIO, E, P>(sx, xf32, nt, tid);
+      if (smx) softmax_rows<TIO, E, P, T>(sx, xf32, nt, tid);
       else convert_rows<TIO, E, P>(sx, xf32, nt, tid);
       __syncthreads();
       sxs = xf32;
@@ -1359,7 +1359,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_det_kernel(const SrwmBwdDetP
     }
     if (smx) {
       __syncthreads();
-      softmax_bwd_rows<TIO, E, P>(sxs, sgx, NWARP * E, p.gx.row(n, h, t0), p.gx.sl, nt, tid);
+      softmax_bwd_rows<TIO, E, P, T>(sxs, sgx, NWARP * E, p.gx.row(n, h, t0), p.gx.sl, nt, tid);
       __syncthreads();   // softmax(x) may sit in the staging buffer the next prefetch overwrites
     }
   }

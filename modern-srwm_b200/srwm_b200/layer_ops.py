@@ -213,6 +213,7 @@ class SrwmLayer(torch.autograd.Function):
             raise ValueError("done (in-kernel state reset) needs detach_state=True: the reverse-time "
                              "backward cannot cross a reset")
         need = any(ctx.needs_input_grad[:9])
+        ctx.set_materialize_grads(False)     # unused outputs arrive as None, not as zero tensors
         out, shift_out, saved = srwm_layer_forward(x, base, shift, done, input_softmax, save=need)
         ctx.cfg = (input_softmax, detach_state, shift is not None, done is not None)
         if need:
