@@ -252,6 +252,53 @@ typedef struct srwm_b200_delta_bwd_args {
 int srwm_b200_delta_backward(const srwm_b200_delta_bwd_args* args, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------
+ * Layer-level delta-rule calls: the kernels read the RAW rows the layers' slow net produces,
+ *   qkvb[n,h,t,:] = [ q (E) | k (E) | v (E) | b (1) ]
+ * (supervised_learning/layer.py:74-77, reinforcement_learning/torchbeast/layer.py:144-147:
+ * `qkvb.view(slen, bsz, num_head, 3*dim_head+1)` split four ways) and do the layers'
+ * preparation themselves:
+ *   q = a(q) / (sum a(q) + norm_eps), k likewise, a(x) = elu(x) + 1;  beta = sigmoid(b)
+ * (layer.py:79,86-90: norm_eps = 0;  torchbeast/layer.py:30-33,156-157: norm_eps = 1e-5).
+ * The backward returns the gradient of the raw rows in the same packed layout.  No reference
+ * function corresponds one to one.  Packed rows need only ELEMENT alignment (any strides);
+ * they are staged as the 16-byte blocks that cover them, so the buffers they live in must be
+ * allocated with 16-byte granularity (every cudaMalloc-family allocation is).
+ * ZERO_INIT (forward): W_0 = 0 and W is not read -- the layers' `torch.zeros` fast weights
+ * (layer.py:92-94) need not be filled; W still receives W_L for the backward.
+ * ---------------------------------------------------------------------------------- */
+#define SRWM_B200_FLAG_ZERO_INIT 16u
+
+typedef struct srwm_b200_delta_packed_fwd_args {
+  int32_t N, H, L, E;
+  int32_t io_dtype;
+  uint32_t flags;                   /* NO_SAVE, ZERO_INIT */
+  int32_t variant;
+  float   norm_eps;
+  srwm_b200_seq   qkvb;             /* in  [N,H,L,3E+1] io_dtype, element-aligned rows */
+  srwm_b200_state W;                /* in/out [N,H,E,E] */
+  srwm_b200_seq   out;              /* out [N,H,L,E] io_dtype */
+  srwm_b200_seq   v_old, v_insert;  /* saved [N,H,L,E] fp32 */
+} srwm_b200_delta_packed_fwd_args;
+
+int srwm_b200_delta_packed_forward(const srwm_b200_delta_packed_fwd_args* args, void* cuda_stream);
+
+typedef struct srwm_b200_delta_packed_bwd_args {
+  int32_t N, H, L, E;
+  int32_t io_dtype;
+  uint32_t flags;
+  int32_t variant;
+  float   norm_eps;
+  srwm_b200_seq   qkvb;             /* in  raw rows, as given to the forward */
+  srwm_b200_seq   v_old, v_insert;  /* in  saved fp32 */
+  srwm_b200_seq   grad_out;         /* in  [N,H,L,E] io_dtype */
+  srwm_b200_state W;                /* in W_L / out W_0 */
+  srwm_b200_seq   grad_qkvb;        /* out [N,H,L,3E+1] io_dtype, element-aligned rows */
+  srwm_b200_state grad_W0;          /* optional out [N,H,E,E] fp32 */
+} srwm_b200_delta_packed_bwd_args;
+
+int srwm_b200_delta_packed_backward(const srwm_b200_delta_packed_bwd_args* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------
  * Batch reduction of per-sample state gradients into the slow-weight gradient:
  *   dst[i] (+)= sum_n src[n*stride_n + i],  i < count   (fp32, deterministic order).
  * This is the backward of the callers' `W.repeat(bsz, 1, 1, 1)`

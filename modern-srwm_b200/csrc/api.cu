@@ -303,8 +303,8 @@ int srwm_b200_delta_forward(const srwm_b200_delta_fwd_args* a, void* stream) {
   if (save) ok = ok && seq_aligned(a->v_old, 4) && seq_aligned(a->v_insert, 4);
   if (!ok) return SRWM_B200_ERR_ALIGN;
 
-  srwm::DeltaFwdParams p;
-  p.N = a->N; p.H = a->H; p.L = a->L; p.flags = a->flags;
+  srwm::DeltaFwdParams p = {};
+  p.N = a->N; p.H = a->H; p.L = a->L; p.flags = a->flags & SRWM_B200_FLAG_NO_SAVE;
   p.Q = view(a->Q, es); p.K = view(a->K, es); p.V = view(a->V, es); p.beta = view(a->beta, es);
   p.out = view(a->out, es); p.v_old = view(a->v_old, 4); p.v_ins = view(a->v_insert, 4);
   p.W = view(a->W);
@@ -335,11 +335,72 @@ int srwm_b200_delta_backward(const srwm_b200_delta_bwd_args* a, void* stream) {
          ((uintptr_t)a->grad_beta.data % es == 0);
   if (!ok) return SRWM_B200_ERR_ALIGN;
 
-  srwm::DeltaBwdParams p;
-  p.N = a->N; p.H = a->H; p.L = a->L; p.flags = a->flags;
+  srwm::DeltaBwdParams p = {};
+  p.N = a->N; p.H = a->H; p.L = a->L; p.flags = 0;
   p.Q = view(a->Q, es); p.K = view(a->K, es); p.V = view(a->V, es); p.beta = view(a->beta, es);
   p.v_old = view(a->v_old, 4); p.v_ins = view(a->v_insert, 4); p.gout = view(a->grad_out, es);
   p.gQ = view(a->grad_Q, es); p.gK = view(a->grad_K, es); p.gV = view(a->grad_V, es); p.gbeta = view(a->grad_beta, es);
+  p.W = view(a->W); p.gW0 = view(a->grad_W0);
+  int ce = 0;
+  const int rc = a->io_dtype == SRWM_B200_BF16
+                     ? srwm::dispatch_delta_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
+                     : srwm::dispatch_delta_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+  return finish(rc, ce);
+}
+
+int srwm_b200_delta_packed_forward(const srwm_b200_delta_packed_fwd_args* a, void* stream) {
+  if (!a) return SRWM_B200_ERR_NULL;
+  long long grid;
+  if (int rc = check_dims(a->N, a->H, a->L, &grid)) return rc;
+  if (!head_dim_ok(a->E)) return SRWM_B200_ERR_HEAD_DIM;
+  if (a->io_dtype != SRWM_B200_F32 && a->io_dtype != SRWM_B200_BF16) return SRWM_B200_ERR_DTYPE;
+  if (grid == 0 || a->L == 0) return 0;
+  const bool save = !(a->flags & SRWM_B200_FLAG_NO_SAVE);
+  if (!a->qkvb.data || !a->W.data || !a->out.data) return SRWM_B200_ERR_NULL;
+  if (save && (!a->v_old.data || !a->v_insert.data)) return SRWM_B200_ERR_NULL;
+  const int es = esize(a->io_dtype);
+  bool ok = ((uintptr_t)a->qkvb.data % es == 0) && seq_aligned(a->out, es) && state_aligned(a->W);
+  if (save) ok = ok && seq_aligned(a->v_old, 4) && seq_aligned(a->v_insert, 4);
+  if (!ok) return SRWM_B200_ERR_ALIGN;
+
+  srwm::DeltaFwdParams p = {};
+  p.N = a->N; p.H = a->H; p.L = a->L;
+  p.flags = (a->flags & SRWM_B200_FLAG_NO_SAVE) | srwm::F_PACKED |
+            ((a->flags & SRWM_B200_FLAG_ZERO_INIT) ? srwm::F_ZERO_INIT : 0u);
+  p.eps = a->norm_eps;
+  p.Q = view(a->qkvb, es);
+  p.out = view(a->out, es); p.v_old = view(a->v_old, 4); p.v_ins = view(a->v_insert, 4);
+  p.W = view(a->W);
+  int ce = 0;
+  const int rc = a->io_dtype == SRWM_B200_BF16
+                     ? srwm::dispatch_delta_fwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
+                     : srwm::dispatch_delta_fwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+  return finish(rc, ce);
+}
+
+int srwm_b200_delta_packed_backward(const srwm_b200_delta_packed_bwd_args* a, void* stream) {
+  if (!a) return SRWM_B200_ERR_NULL;
+  long long grid;
+  if (int rc = check_dims(a->N, a->H, a->L, &grid)) return rc;
+  if (!head_dim_ok(a->E)) return SRWM_B200_ERR_HEAD_DIM;
+  if (a->io_dtype != SRWM_B200_F32 && a->io_dtype != SRWM_B200_BF16) return SRWM_B200_ERR_DTYPE;
+  if (grid == 0) return 0;
+  if (!a->W.data) return SRWM_B200_ERR_NULL;
+  if (a->L > 0 && (!a->qkvb.data || !a->v_old.data || !a->v_insert.data || !a->grad_out.data || !a->grad_qkvb.data))
+    return SRWM_B200_ERR_NULL;
+  const int es = esize(a->io_dtype);
+  bool ok = state_aligned(a->W) && (a->grad_W0.data == nullptr || state_aligned(a->grad_W0));
+  if (a->L > 0)
+    ok = ok && ((uintptr_t)a->qkvb.data % es == 0) && ((uintptr_t)a->grad_qkvb.data % es == 0) &&
+         seq_aligned(a->grad_out, es) && seq_aligned(a->v_old, 4) && seq_aligned(a->v_insert, 4);
+  if (!ok) return SRWM_B200_ERR_ALIGN;
+
+  srwm::DeltaBwdParams p = {};
+  p.N = a->N; p.H = a->H; p.L = a->L;
+  p.flags = srwm::F_PACKED;
+  p.eps = a->norm_eps;
+  p.Q = view(a->qkvb, es); p.gQ = view(a->grad_qkvb, es);
+  p.v_old = view(a->v_old, 4); p.v_ins = view(a->v_insert, 4); p.gout = view(a->grad_out, es);
   p.W = view(a->W); p.gW0 = view(a->grad_W0);
   int ce = 0;
   const int rc = a->io_dtype == SRWM_B200_BF16

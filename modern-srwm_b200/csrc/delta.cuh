@@ -8,38 +8,118 @@
 // the P threads of one CTA (see common.cuh); there is no block-wide barrier inside the
 // time loop of either kernel -- only warp shuffles.
 #pragma once
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace srwm {
 
+// The packed (layer-level) form, selected by F_PACKED: instead of four prepared tensors the
+// kernels read the raw rows [q | k | v | b] (3E+1 values) that the layers' slow net produces
+// (supervised_learning/layer.py:74-77, reinforcement_learning/torchbeast/layer.py:144-147) and
+// apply the layers' preparation themselves, per staged chunk:
+//   q = a(q) / (sum a(q) + eps),  k likewise,  a(x) = elu(x) + 1 ;  beta = sigmoid(b)
+// (layer.py:79, 86-90 with eps = 0; torchbeast/layer.py:30-33 with eps = 1e-5).  The backward
+// returns the gradient of the raw rows in the same packed layout.  Rows only need element
+// alignment: they are staged as the 16-byte blocks that cover them.
+constexpr unsigned F_PACKED = 8u, F_ZERO_INIT = 16u;
+
 struct DeltaFwdParams {
   int N, H, L;
   unsigned flags;
-  SeqView Q, K, V, beta, out, v_old, v_ins;
+  SeqView Q, K, V, beta, out, v_old, v_ins;   // Q doubles as the packed rows
   StateView W;
+  float eps;
 };
 
 struct DeltaBwdParams {
   int N, H, L;
   unsigned flags;
-  SeqView Q, K, V, beta, v_old, v_ins, gout, gQ, gK, gV, gbeta;
+  SeqView Q, K, V, beta, v_old, v_ins, gout, gQ, gK, gV, gbeta;   // Q / gQ double as the packed rows
   StateView W, gW0;
+  float eps;
 };
 
-template <typename TIO, int E, int T>
+__device__ __forceinline__ float elu_p1(float x) { return x > 0.f ? x + 1.f : __expf(x); }
+
+// Stage nt packed rows of RSB bytes each: every row as the 16-byte blocks covering it
+// (row r lands at dst + r*PITCH, its first byte at offset (address & 15) inside).
+template <int RSB, int PITCH, int P>
+__device__ __forceinline__ void stage_packed_rows(unsigned char* dst, const char* row0, long long row_stride_bytes,
+                                                  int nt, int tid) {
+  constexpr int NB = PITCH / 16;
+  for (int idx = tid; idx < nt * NB; idx += P) {
+    const int r = idx / NB, blk = idx % NB;
+    const char* a = row0 + r * row_stride_bytes;
+    const int off = (int)(reinterpret_cast<uintptr_t>(a) & 15);
+    if (blk * 16 < off + RSB) cp_async16(dst + r * PITCH + blk * 16, a - off + blk * 16);
+  }
+}
+
+// The layers' preparation of a staged chunk of packed rows: dense fp32 q, k (normalised), v and
+// beta rows; optionally the normalisers (sum + eps) for the backward.  A row is handled by E/4
+// adjacent lanes (4 values of each of q, k, v per lane).
+template <typename TIO, int E, int P, int T, int PITCH>
+__device__ __forceinline__ void prepare_packed_rows(const unsigned char* raw, const char* row0,
+                                                    long long row_stride_bytes, float eps, float* dq, float* dk,
+                                                    float* dv, float* db, float* dsq, float* dsk, int nt, int tid) {
+  constexpr int LPR = E / 4, NG = P / LPR, K = (T + NG - 1) / NG;
+  const int grp = tid / LPR, l = tid % LPR;
+#pragma unroll
+  for (int kk = 0; kk < K; ++kk) {
+    const int t = grp + kk * NG;
+    const int tc = min(t, nt - 1);
+    const int off = (int)(reinterpret_cast<uintptr_t>(row0 + tc * row_stride_bytes) & 15);
+    const TIO* r = reinterpret_cast<const TIO*>(raw + tc * PITCH + off);
+    float q[4], k[4], v[4], sq = 0.f, sk = 0.f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      q[i] = elu_p1(to_f32(r[l * 4 + i]));
+      k[i] = elu_p1(to_f32(r[E + l * 4 + i]));
+      v[i] = to_f32(r[2 * E + l * 4 + i]);
+      sq += q[i];
+      sk += k[i];
+    }
+#pragma unroll
+    for (int o = 1; o < LPR; o <<= 1) {
+      sq += __shfl_xor_sync(0xffffffffu, sq, o);
+      sk += __shfl_xor_sync(0xffffffffu, sk, o);
+    }
+    sq += eps;
+    sk += eps;
+    const float iq = __fdividef(1.f, sq), ik = __fdividef(1.f, sk);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { q[i] *= iq; k[i] *= ik; }
+    if (t < nt) {
+      st_vec<4>(dq + t * E + l * 4, q);
+      st_vec<4>(dk + t * E + l * 4, k);
+      st_vec<4>(dv + t * E + l * 4, v);
+      if (l == 0) {
+        db[t] = fast_sigmoid(to_f32(r[3 * E]));
+        if (dsq) { dsq[t] = sq; dsk[t] = sk; }
+      }
+    }
+  }
+}
+
+template <typename TIO, int E, int T, bool PACKED = false>
 struct DeltaFwdSmem {
   static constexpr int ROW_IO = E * (int)sizeof(TIO);
   static constexpr int ROW_F = E * 4;
   static constexpr int BETA_BYTES = ((T * 4 + 15) / 16) * 16;
-  static constexpr int IN_BYTES = 3 * T * ROW_IO + BETA_BYTES;   // q,k,v,beta of one buffer
+  static constexpr int RSB = (3 * E + 1) * (int)sizeof(TIO);     // bytes of a packed row
+  static constexpr int PK_PITCH = ((RSB + 30) / 16) * 16;        // the 16-byte blocks that can cover it
+  static constexpr int IN_BYTES = PACKED ? T * PK_PITCH : 3 * T * ROW_IO + BETA_BYTES;   // one staging buffer
+  static constexpr int DENSE_BYTES = PACKED ? 3 * T * ROW_F + BETA_BYTES : 0;   // prepared q,k,v,beta (fp32)
   static constexpr int OUT_BYTES = T * ROW_IO + 2 * T * ROW_F;   // out, v_old, v_ins
-  static constexpr int TOTAL = 2 * IN_BYTES + OUT_BYTES;
+  static constexpr int TOTAL = 2 * IN_BYTES + DENSE_BYTES + OUT_BYTES;
 };
 
-template <typename TIO, int E, int P, int R, int T, bool PK, int MINB>
+template <typename TIO, int E, int P, int R, int T, bool PK, int MINB, bool PACKED = false>
 __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams p) {
   using TL = Tiling<E, P, R>;
-  using SM = DeltaFwdSmem<TIO, E, T>;
+  using SM = DeltaFwdSmem<TIO, E, T, PACKED>;
+  using TS = typename std::conditional<PACKED, float, TIO>::type;   // element type the step loop reads
   constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2;
   const int tid = threadIdx.x;
   const int rg = tid % NRG, cg = tid / NRG;
@@ -47,7 +127,8 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
   const bool save = !(p.flags & 1u);
 
   extern __shared__ __align__(16) unsigned char smem[];
-  unsigned char* s_out = smem + 2 * SM::IN_BYTES;
+  float* dense = reinterpret_cast<float*>(smem + 2 * SM::IN_BYTES);   // PACKED: q | k | v | beta
+  unsigned char* s_out = smem + 2 * SM::IN_BYTES + SM::DENSE_BYTES;
   TIO* so = reinterpret_cast<TIO*>(s_out);
   float* svold = reinterpret_cast<float*>(s_out + T * SM::ROW_IO);
   float* svins = svold + T * E;
@@ -55,11 +136,17 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
   // state tile
   u64 W[R2][C];
   float* Wg = p.W.mat(n, h);
+  const bool zero_init = PACKED && (p.flags & F_ZERO_INIT);
 #pragma unroll
   for (int i2 = 0; i2 < R2; ++i2) {
     float a[C], b[C];
-    ld_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
-    ld_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
+    if (zero_init) {
+#pragma unroll
+      for (int j = 0; j < C; ++j) { a[j] = 0.f; b[j] = 0.f; }
+    } else {
+      ld_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2)) * E + cg * C, a);
+      ld_vec<C>(Wg + (row_of<R, NRG>(rg, 2 * i2 + 1)) * E + cg * C, b);
+    }
 #pragma unroll
     for (int j = 0; j < C; ++j) W[i2][j] = pack2(a[j], b[j]);
   }
@@ -70,9 +157,13 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
     unsigned char* ib = in_buf(c & 1);
-    stage_rows<SM::ROW_IO, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, tid);
-    stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.K.row(n, h, t0), p.K.sl, nt, tid);
-    stage_rows<SM::ROW_IO, P>(ib + 2 * T * SM::ROW_IO, p.V.row(n, h, t0), p.V.sl, nt, tid);
+    if constexpr (PACKED) {
+      stage_packed_rows<SM::RSB, SM::PK_PITCH, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, tid);
+    } else {
+      stage_rows<SM::ROW_IO, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, tid);
+      stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.K.row(n, h, t0), p.K.sl, nt, tid);
+      stage_rows<SM::ROW_IO, P>(ib + 2 * T * SM::ROW_IO, p.V.row(n, h, t0), p.V.sl, nt, tid);
+    }
   };
   auto beta_ld = [&](int c, int i) -> float {   // i-th step of chunk c (plain load: rows are 1 element)
     return to_f32(*reinterpret_cast<const TIO*>(p.beta.row(n, h, c * T + i)));
@@ -81,7 +172,8 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
 
   stage_chunk(0);
   cp_async_commit();
-  for (int i = tid; i < min(T, L); i += P) beta_buf(0)[i] = beta_ld(0, i);
+  if constexpr (!PACKED)
+    for (int i = tid; i < min(T, L); i += P) beta_buf(0)[i] = beta_ld(0, i);
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * T, nt = min(T, L - t0);
@@ -90,10 +182,12 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
     float bnext[(T + P - 1) / P];
     if (has_next) {
       stage_chunk(c + 1);
+      if constexpr (!PACKED) {
 #pragma unroll
-      for (int u = 0; u < (T + P - 1) / P; ++u) {
-        const int i = tid + u * P;
-        bnext[u] = (i < nt_next) ? beta_ld(c + 1, i) : 0.f;
+        for (int u = 0; u < (T + P - 1) / P; ++u) {
+          const int i = tid + u * P;
+          bnext[u] = (i < nt_next) ? beta_ld(c + 1, i) : 0.f;
+        }
       }
     }
     cp_async_commit();
@@ -101,10 +195,20 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
     __syncthreads();
 
     const unsigned char* ib = in_buf(c & 1);
-    const TIO* sq = reinterpret_cast<const TIO*>(ib);
-    const TIO* sk = reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO);
-    const TIO* sv = reinterpret_cast<const TIO*>(ib + 2 * T * SM::ROW_IO);
-    const float* sb = beta_buf(c & 1);
+    const TS *sq, *sk, *sv;
+    const float* sb;
+    if constexpr (PACKED) {
+      float* dq = dense;
+      prepare_packed_rows<TIO, E, P, T, SM::PK_PITCH>(ib, p.Q.row(n, h, t0), p.Q.sl, p.eps, dq, dq + T * E,
+                                                      dq + 2 * T * E, dq + 3 * T * E, nullptr, nullptr, nt, tid);
+      __syncthreads();
+      sq = dq; sk = dq + T * E; sv = dq + 2 * T * E; sb = dq + 3 * T * E;
+    } else {
+      sq = reinterpret_cast<const TS*>(ib);
+      sk = reinterpret_cast<const TS*>(ib + T * SM::ROW_IO);
+      sv = reinterpret_cast<const TS*>(ib + 2 * T * SM::ROW_IO);
+      sb = beta_buf(c & 1);
+    }
 
     #pragma unroll 1
 
@@ -156,11 +260,13 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
       }
     }
 
-    if (has_next) {
+    if constexpr (!PACKED) {
+      if (has_next) {
 #pragma unroll
-      for (int u = 0; u < (T + P - 1) / P; ++u) {
-        const int i = tid + u * P;
-        if (i < nt_next) beta_buf((c + 1) & 1)[i] = bnext[u];
+        for (int u = 0; u < (T + P - 1) / P; ++u) {
+          const int i = tid + u * P;
+          if (i < nt_next) beta_buf((c + 1) & 1)[i] = bnext[u];
+        }
       }
     }
     __syncthreads();
@@ -192,24 +298,29 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
 // shared memory and summed across warps when the chunk is written out -- they are outputs
 // only, so nothing on the recurrence's critical path waits for a barrier.
 // ---------------------------------------------------------------------------------------
-template <typename TIO, int E, int P, int T>
+template <typename TIO, int E, int P, int T, bool PACKED = false>
 struct DeltaBwdSmem {
   static constexpr int NWARP = P / 32;
   static constexpr int ROW_IO = E * (int)sizeof(TIO);
   static constexpr int ROW_F = E * 4;
   static constexpr int BETA_BYTES = ((T * 4 + 15) / 16) * 16;
-  // q,k,v,gout (io) + v_old, v_ins (f32) + beta
-  static constexpr int IN_BYTES = 4 * T * ROW_IO + 2 * T * ROW_F + BETA_BYTES;
+  static constexpr int RSB = (3 * E + 1) * (int)sizeof(TIO);
+  static constexpr int PK_PITCH = ((RSB + 30) / 16) * 16;
+  // q,k,v (io, or the packed rows) | gout (io) | v_old, v_ins (f32) | beta
+  static constexpr int QKV_BYTES = PACKED ? T * PK_PITCH : 3 * T * ROW_IO;
+  static constexpr int IN_BYTES = QKV_BYTES + T * ROW_IO + 2 * T * ROW_F + (PACKED ? 0 : BETA_BYTES);
+  static constexpr int DENSE_BYTES = PACKED ? 3 * T * ROW_F + 3 * BETA_BYTES : 0;   // q,k,v | beta, sum_q, sum_k
   static constexpr int GV_BYTES = T * ROW_IO;
   static constexpr int PART_BYTES = T * NWARP * 2 * ROW_F;       // per-warp partial gq, gk
   static constexpr int GB_BYTES = ((T * NWARP * 4 + 15) / 16) * 16;
-  static constexpr int TOTAL = 2 * IN_BYTES + GV_BYTES + PART_BYTES + GB_BYTES;
+  static constexpr int TOTAL = 2 * IN_BYTES + GV_BYTES + PART_BYTES + GB_BYTES + DENSE_BYTES;
 };
 
-template <typename TIO, int E, int P, int R, int T, bool PK, int MINB>
+template <typename TIO, int E, int P, int R, int T, bool PK, int MINB, bool PACKED = false>
 __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams p) {
   using TL = Tiling<E, P, R>;
-  using SM = DeltaBwdSmem<TIO, E, P, T>;
+  using SM = DeltaBwdSmem<TIO, E, P, T, PACKED>;
+  using TS = typename std::conditional<PACKED, float, TIO>::type;
   constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2, NWARP = TL::NWARP, CGW = TL::CGW;
   // row sums leave the warp through a reduce-scatter when the tile shape allows it
   constexpr bool SCATTER = (CGW >= 2) && ((2 * R) % CGW == 0) && ((2 * R) / CGW <= 4 || ((2 * R) / CGW) % 4 == 0);
@@ -225,6 +336,7 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
   TIO* sgv = reinterpret_cast<TIO*>(s_o);
   float* spart = reinterpret_cast<float*>(s_o + SM::GV_BYTES);          // [T][NWARP][2][E]
   float* sgb = reinterpret_cast<float*>(s_o + SM::GV_BYTES + SM::PART_BYTES);  // [T][NWARP]
+  float* dense = reinterpret_cast<float*>(s_o + SM::GV_BYTES + SM::PART_BYTES + SM::GB_BYTES);   // PACKED
 
   u64 W[R2][C], G[R2][C];
   float* Wg = p.W.mat(n, h);
@@ -243,11 +355,15 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
     unsigned char* ib = in_buf(c & 1);
-    stage_rows<SM::ROW_IO, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, tid);
-    stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.K.row(n, h, t0), p.K.sl, nt, tid);
-    stage_rows<SM::ROW_IO, P>(ib + 2 * T * SM::ROW_IO, p.V.row(n, h, t0), p.V.sl, nt, tid);
-    stage_rows<SM::ROW_IO, P>(ib + 3 * T * SM::ROW_IO, p.gout.row(n, h, t0), p.gout.sl, nt, tid);
-    unsigned char* fb = ib + 4 * T * SM::ROW_IO;
+    if constexpr (PACKED) {
+      stage_packed_rows<SM::RSB, SM::PK_PITCH, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, tid);
+    } else {
+      stage_rows<SM::ROW_IO, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, tid);
+      stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.K.row(n, h, t0), p.K.sl, nt, tid);
+      stage_rows<SM::ROW_IO, P>(ib + 2 * T * SM::ROW_IO, p.V.row(n, h, t0), p.V.sl, nt, tid);
+    }
+    stage_rows<SM::ROW_IO, P>(ib + SM::QKV_BYTES, p.gout.row(n, h, t0), p.gout.sl, nt, tid);
+    unsigned char* fb = ib + SM::QKV_BYTES + T * SM::ROW_IO;
     stage_rows<SM::ROW_F, P>(fb, p.v_old.row(n, h, t0), p.v_old.sl, nt, tid);
     stage_rows<SM::ROW_F, P>(fb + T * SM::ROW_F, p.v_ins.row(n, h, t0), p.v_ins.sl, nt, tid);
   };
@@ -255,7 +371,7 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
     return to_f32(*reinterpret_cast<const TIO*>(p.beta.row(n, h, c * T + i)));
   };
   auto beta_buf = [&](int b) {
-    return reinterpret_cast<float*>(in_buf(b) + 4 * T * SM::ROW_IO + 2 * T * SM::ROW_F);
+    return reinterpret_cast<float*>(in_buf(b) + SM::QKV_BYTES + T * SM::ROW_IO + 2 * T * SM::ROW_F);
   };
 
   {
@@ -263,7 +379,8 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
     stage_chunk(c0);
     cp_async_commit();
     const int nt0 = L - c0 * T;
-    for (int i = tid; i < nt0; i += P) beta_buf(c0 & 1)[i] = beta_ld(c0, i);
+    if constexpr (!PACKED)
+      for (int i = tid; i < nt0; i += P) beta_buf(c0 & 1)[i] = beta_ld(c0, i);
   }
 
   for (int c = nchunks - 1; c >= 0; --c) {
@@ -272,10 +389,12 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
     float bnext[(T + P - 1) / P];
     if (has_next) {
       stage_chunk(c - 1);   // full chunk of T steps
+      if constexpr (!PACKED) {
 #pragma unroll
-      for (int u = 0; u < (T + P - 1) / P; ++u) {
-        const int i = tid + u * P;
-        bnext[u] = (i < T) ? beta_ld(c - 1, i) : 0.f;
+        for (int u = 0; u < (T + P - 1) / P; ++u) {
+          const int i = tid + u * P;
+          bnext[u] = (i < T) ? beta_ld(c - 1, i) : 0.f;
+        }
       }
     }
     cp_async_commit();
@@ -283,13 +402,25 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
     __syncthreads();
 
     const unsigned char* ib = in_buf(c & 1);
-    const TIO* sq = reinterpret_cast<const TIO*>(ib);
-    const TIO* sk = reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO);
-    const TIO* sv = reinterpret_cast<const TIO*>(ib + 2 * T * SM::ROW_IO);
-    const TIO* sg = reinterpret_cast<const TIO*>(ib + 3 * T * SM::ROW_IO);
-    const float* svo = reinterpret_cast<const float*>(ib + 4 * T * SM::ROW_IO);
+    const TS *sq, *sk, *sv;
+    const float* sb;
+    float* dsq = dense + 3 * T * E + SM::BETA_BYTES / 4;   // PACKED: sum a(q) + eps, sum a(k) + eps per row
+    float* dsk = dsq + SM::BETA_BYTES / 4;
+    if constexpr (PACKED) {
+      float* dq = dense;
+      prepare_packed_rows<TIO, E, P, T, SM::PK_PITCH>(ib, p.Q.row(n, h, t0), p.Q.sl, p.eps, dq, dq + T * E,
+                                                      dq + 2 * T * E, dq + 3 * T * E, dsq, dsk, nt, tid);
+      __syncthreads();
+      sq = dq; sk = dq + T * E; sv = dq + 2 * T * E; sb = dq + 3 * T * E;
+    } else {
+      sq = reinterpret_cast<const TS*>(ib);
+      sk = reinterpret_cast<const TS*>(ib + T * SM::ROW_IO);
+      sv = reinterpret_cast<const TS*>(ib + 2 * T * SM::ROW_IO);
+      sb = beta_buf(c & 1);
+    }
+    const TIO* sg = reinterpret_cast<const TIO*>(ib + SM::QKV_BYTES);
+    const float* svo = reinterpret_cast<const float*>(ib + SM::QKV_BYTES + T * SM::ROW_IO);
     const float* svi = svo + T * E;
-    const float* sb = beta_buf(c & 1);
 
     #pragma unroll 1
 
@@ -375,15 +506,17 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
       if (lane == 0) sgb[t * NWARP + warp] = gb;
     }
 
-    if (has_next) {
+    if constexpr (!PACKED) {
+      if (has_next) {
 #pragma unroll
-      for (int u = 0; u < (T + P - 1) / P; ++u) {
-        const int i = tid + u * P;
-        if (i < T) beta_buf((c - 1) & 1)[i] = bnext[u];
+        for (int u = 0; u < (T + P - 1) / P; ++u) {
+          const int i = tid + u * P;
+          if (i < T) beta_buf((c - 1) & 1)[i] = bnext[u];
+        }
       }
     }
     __syncthreads();
-    flush_rows<SM::ROW_IO, P>(p.gV.row(n, h, t0), p.gV.sl, sgv, nt, tid);
+    if constexpr (!PACKED) flush_rows<SM::ROW_IO, P>(p.gV.row(n, h, t0), p.gV.sl, sgv, nt, tid);
     // combine the per-warp partial rows and write gq, gk (4 values per thread-iteration)
     for (int idx = tid; idx < nt * 2 * (E / 4); idx += P) {
       const int e4 = idx % (E / 4);
@@ -397,14 +530,67 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
 #pragma unroll
         for (int u = 0; u < 4; ++u) acc[u] += v[u];
       }
-      const SeqView& dstv = which ? p.gK : p.gQ;
-      st_vec<4>(reinterpret_cast<TIO*>(dstv.row(n, h, t0 + t)) + e4 * 4, acc);
+      if constexpr (PACKED) {
+        st_vec<4>(spart + ((t * NWARP) * 2 + which) * E + e4 * 4, acc);   // finished below
+      } else {
+        const SeqView& dstv = which ? p.gK : p.gQ;
+        st_vec<4>(reinterpret_cast<TIO*>(dstv.row(n, h, t0 + t)) + e4 * 4, acc);
+      }
     }
-    for (int t = tid; t < nt; t += P) {
-      float s = 0.f;
+    if constexpr (PACKED) {
+      // back through the layers' preparation, into the packed gradient row [gq | gk | gv | gb]:
+      //   q = a / S  =>  ga = (gq - gq.q) / S ;  a = elu(x) + 1  =>  gx = ga * (x > 0 ? 1 : a), x > 0 <=> a > 1
+      __syncthreads();
+      constexpr int LPR = E / 4, NG = P / LPR, K = (T + NG - 1) / NG;
+      const int grp = tid / LPR, l = tid % LPR;
 #pragma unroll
-      for (int w = 0; w < NWARP; ++w) s += sgb[t * NWARP + w];
-      from_f32(*reinterpret_cast<TIO*>(p.gbeta.row(n, h, t0 + t)), s);
+      for (int kk = 0; kk < K; ++kk) {
+        const int t = grp + kk * NG;
+        const int tc = min(t, nt - 1);
+        float gq[4], gk[4], q[4], k[4], gv[4];
+        ld_vec<4>(spart + ((tc * NWARP) * 2) * E + l * 4, gq);
+        ld_vec<4>(spart + ((tc * NWARP) * 2 + 1) * E + l * 4, gk);
+        ld_vec<4>(sq + tc * E + l * 4, q);
+        ld_vec<4>(sk + tc * E + l * 4, k);
+        ld_vec<4>(sgv + tc * E + l * 4, gv);
+        float dq_ = 0.f, dk_ = 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          dq_ = fmaf(gq[i], q[i], dq_);
+          dk_ = fmaf(gk[i], k[i], dk_);
+        }
+#pragma unroll
+        for (int o = 1; o < LPR; o <<= 1) {
+          dq_ += __shfl_xor_sync(0xffffffffu, dq_, o);
+          dk_ += __shfl_xor_sync(0xffffffffu, dk_, o);
+        }
+        const float Sq = dsq[tc], Sk = dsk[tc];
+        const float iq = __fdividef(1.f, Sq), ik = __fdividef(1.f, Sk);
+        if (t < nt) {
+          TIO* g = reinterpret_cast<TIO*>(p.gQ.row(n, h, t0 + t));
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float aq = q[i] * Sq, ak = k[i] * Sk;
+            from_f32(g[l * 4 + i], (gq[i] - dq_) * iq * (aq > 1.f ? 1.f : aq));
+            from_f32(g[E + l * 4 + i], (gk[i] - dk_) * ik * (ak > 1.f ? 1.f : ak));
+            from_f32(g[2 * E + l * 4 + i], gv[i]);
+          }
+          if (l == 0) {
+            float sgbv = 0.f;
+#pragma unroll
+            for (int w = 0; w < NWARP; ++w) sgbv += sgb[t * NWARP + w];
+            const float b = sb[t];
+            from_f32(g[3 * E], sgbv * b * (1.f - b));
+          }
+        }
+      }
+    } else {
+      for (int t = tid; t < nt; t += P) {
+        float s = 0.f;
+#pragma unroll
+        for (int w = 0; w < NWARP; ++w) s += sgb[t * NWARP + w];
+        from_f32(*reinterpret_cast<TIO*>(p.gbeta.row(n, h, t0 + t)), s);
+      }
     }
   }
 

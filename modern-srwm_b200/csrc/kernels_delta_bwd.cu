@@ -12,8 +12,21 @@ typedef __nv_bfloat16 TIO;
 typedef float TIO;
 #endif
 
-template <int E, int P, int R, int T, bool PK, int MINB>
+// The packed (layer-level) form of a call runs the PACKED instantiation of the default
+// configuration; the plain form keeps its own, unchanged code.
+template <int E, int V, int P, int R, int T, bool PK, int MINB>
 int run(const DeltaBwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
+  if (p.flags & F_PACKED) {
+    if constexpr (V == 0) {
+      constexpr int smem = DeltaBwdSmem<TIO, E, P, T, true>::TOTAL;
+      if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; }
+      if (describe_only) return 0;
+      static unsigned long long dev_mask_pk = 0;
+      return launch_kernel(delta_bwd_kernel<TIO, E, P, R, T, PK, MINB, true>, p, grid, P, smem, s, &dev_mask_pk, cuda_err);
+    } else {
+      return -6;
+    }
+  }
   constexpr int smem = DeltaBwdSmem<TIO, E, P, T>::TOTAL;
   if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; }
   if (describe_only) return 0;
@@ -31,7 +44,7 @@ int dispatch_delta_bwd_f32(
     int E, int variant, const DeltaBwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only,
     int* cuda_err) {
 #define X(E_, V_, P_, R_, T_, PK_, MINB_) \
-  if (E == E_ && variant == V_) return run<E_, P_, R_, T_, PK_, MINB_>(p, grid, s, info, describe_only, cuda_err);
+  if (E == E_ && variant == V_) return run<E_, V_, P_, R_, T_, PK_, MINB_>(p, grid, s, info, describe_only, cuda_err);
   DELTA_BWD_CONFIGS(X)
 #undef X
   return (E == 8 || E == 16 || E == 32 || E == 64) ? -6 : -3;

@@ -13,7 +13,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libsrwm_b200.so")
 
 F32, BF16 = 0, 1
-FLAG_NO_SAVE, FLAG_STATE_GRAD_IN, FLAG_RESTORE_STATE, FLAG_INPUT_SOFTMAX = 1, 2, 4, 8
+FLAG_NO_SAVE, FLAG_STATE_GRAD_IN, FLAG_RESTORE_STATE, FLAG_INPUT_SOFTMAX, FLAG_ZERO_INIT = 1, 2, 4, 8, 16
 OP_SRWM_FWD, OP_SRWM_BWD, OP_DELTA_FWD, OP_DELTA_BWD, OP_SRWM_BWD_DET = 0, 1, 2, 3, 4
 ABI_VERSION = 2
 
@@ -85,6 +85,21 @@ class DeltaBwdArgs(C.Structure):
                 ("grad_W0", State)]
 
 
+class DeltaPackedFwdArgs(C.Structure):
+    _fields_ = [("N", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("E", C.c_int32),
+                ("io_dtype", C.c_int32), ("flags", C.c_uint32), ("variant", C.c_int32),
+                ("norm_eps", C.c_float),
+                ("qkvb", Seq), ("W", State), ("out", Seq), ("v_old", Seq), ("v_insert", Seq)]
+
+
+class DeltaPackedBwdArgs(C.Structure):
+    _fields_ = [("N", C.c_int32), ("H", C.c_int32), ("L", C.c_int32), ("E", C.c_int32),
+                ("io_dtype", C.c_int32), ("flags", C.c_uint32), ("variant", C.c_int32),
+                ("norm_eps", C.c_float),
+                ("qkvb", Seq), ("v_old", Seq), ("v_insert", Seq), ("grad_out", Seq), ("W", State),
+                ("grad_qkvb", Seq), ("grad_W0", State)]
+
+
 # name -> (restype, argtypes); also the list of symbols the header declares.
 SYMBOLS = {
     "srwm_b200_srwm_forward": (C.c_int, [C.POINTER(SrwmFwdArgs), C.c_void_p]),
@@ -94,6 +109,8 @@ SYMBOLS = {
     "srwm_b200_srwm_backward_detached": (C.c_int, [C.POINTER(SrwmBwdDetArgs), C.c_void_p]),
     "srwm_b200_delta_forward": (C.c_int, [C.POINTER(DeltaFwdArgs), C.c_void_p]),
     "srwm_b200_delta_backward": (C.c_int, [C.POINTER(DeltaBwdArgs), C.c_void_p]),
+    "srwm_b200_delta_packed_forward": (C.c_int, [C.POINTER(DeltaPackedFwdArgs), C.c_void_p]),
+    "srwm_b200_delta_packed_backward": (C.c_int, [C.POINTER(DeltaPackedBwdArgs), C.c_void_p]),
     "srwm_b200_reduce_batch": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_void_p,
                                          C.c_int32, C.c_void_p]),
     "srwm_b200_abi_version": (C.c_int, []),

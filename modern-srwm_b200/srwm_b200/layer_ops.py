@@ -23,6 +23,14 @@ the initial shift the per-sample dL/dW_0.  ``detach_state=True``: the reference 
 gradient, i.e. every step sees a detached state (torchbeast/layer.py:412-421): only W_y and x
 receive gradient, W_q / W_k / w_b get zeros; required when ``done`` is given.
 
+    delta_layer(qkvb, W, norm_eps=0.0, zero_init=False) -> out
+
+is the same for the delta-rule layers (``FastFFlayer``, supervised_learning/layer.py:49-108 and
+reinforcement_learning/torchbeast/layer.py:127-189): it reads the raw ``slow_net`` rows
+``[q | k | v | b]`` in place -- no split copies -- applies ``elu + 1``, the sum normalisation
+(``norm_eps`` = 0 in the supervised layer, 1e-5 in the agents') and the sigmoid inside the
+kernels, and returns the gradient of the raw rows in the same packed layout.
+
 CUDA tensors only; there is no CPU implementation.
 """
 from __future__ import annotations
@@ -283,3 +291,105 @@ def srwm_layer(x, W_y, W_q, W_k, w_b, shift=None, done=None, input_softmax=True,
     s = (None, None, None, None) if shift is None else tuple(shift)
     res = SrwmLayer.apply(x, W_y, W_q, W_k, w_b, *s, done, bool(input_softmax), bool(detach_state))
     return res[0], tuple(res[1:])
+
+
+# ---------------------------------------------------------------------------------------
+# delta rule on the packed slow-net rows
+# ---------------------------------------------------------------------------------------
+
+def _packed_ok(t):
+    return t.stride(3) == 1 or t.size(3) == 1
+
+
+def delta_packed_forward(qkvb, W, norm_eps=0.0, zero_init=False, save=True):
+    """qkvb [N,H,L,3E+1] view of the raw rows (any strides, contiguous rows); W [N,H,E,E] fp32
+    in/out (not read with ``zero_init``).  Returns (out [N,H,L,E], saved or None)."""
+    _require_cuda(qkvb, W)
+    N, H, Ln, RS = qkvb.shape
+    E = (RS - 1) // 3
+    assert RS == 3 * E + 1 and W.shape == (N, H, E, E)
+    dt = _io_dtype(qkvb)
+    xs = qkvb.detach()
+    if not _packed_ok(xs):
+        xs = xs.contiguous()
+    assert _state_ok(W), "the fast-weight state must be a dense fp32 tensor"
+    dev = qkvb.device
+    out = _like(xs, E)
+    a = L.DeltaPackedFwdArgs()
+    a.N, a.H, a.L, a.E = N, H, Ln, E
+    a.io_dtype = dt
+    a.flags = (0 if save else L.FLAG_NO_SAVE) | (L.FLAG_ZERO_INIT if zero_init else 0)
+    a.variant = 0
+    a.norm_eps = float(norm_eps)
+    a.qkvb = _seq_desc(xs)
+    a.W = _state_desc(W)
+    a.out = _seq_desc(out)
+    saved = None
+    if save:
+        v_old, v_ins = torch.empty((2, N, H, Ln, E), device=dev, dtype=torch.float32).unbind(0)
+        saved = (v_old, v_ins)
+        a.v_old, a.v_insert = _seq_desc(v_old), _seq_desc(v_ins)
+    else:
+        a.v_old = a.v_insert = _NULL_SEQ
+    if Ln == 0 and zero_init:
+        W.zero_()
+    with torch.cuda.device(dev):
+        L.check(L.load().srwm_b200_delta_packed_forward(C.byref(a), _stream(qkvb)), "delta_packed_forward")
+    return out, saved
+
+
+def delta_packed_backward(qkvb, saved, grad_out, W, norm_eps=0.0, want_grad_W0=False):
+    """W holds W_L on entry and W_0 on return.  Returns (grad_qkvb laid out like qkvb, grad_W0 or None)."""
+    _require_cuda(qkvb, grad_out, W)
+    N, H, Ln, RS = qkvb.shape
+    E = (RS - 1) // 3
+    dt = _io_dtype(qkvb)
+    v_old, v_ins = saved
+    xs = qkvb.detach()
+    if not _packed_ok(xs):
+        xs = xs.contiguous()
+    go = _seq(grad_out.detach().to(qkvb.dtype))
+    dev = qkvb.device
+    gx = torch.empty_like(xs)
+    gW0 = torch.empty((N, H, E, E), device=dev, dtype=torch.float32) if want_grad_W0 else None
+    a = L.DeltaPackedBwdArgs()
+    a.N, a.H, a.L, a.E = N, H, Ln, E
+    a.io_dtype = dt
+    a.flags = 0
+    a.variant = 0
+    a.norm_eps = float(norm_eps)
+    a.qkvb = _seq_desc(xs)
+    a.v_old, a.v_insert = _seq_desc(v_old), _seq_desc(v_ins)
+    a.grad_out = _seq_desc(go)
+    a.W = _state_desc(W)
+    a.grad_qkvb = _seq_desc(gx)
+    a.grad_W0 = _state_desc(gW0) if want_grad_W0 else _NULL_STATE
+    with torch.cuda.device(dev):
+        L.check(L.load().srwm_b200_delta_packed_backward(C.byref(a), _stream(qkvb)), "delta_packed_backward")
+    return gx, gW0
+
+
+class DeltaLayer(torch.autograd.Function):
+    """Autograd boundary of :func:`delta_layer` (no gradient for the state, as in
+    ``DeltaFastWeight``, supervised_learning/fast_weight/__init__.py:96)."""
+
+    @staticmethod
+    def forward(ctx, qkvb, W, norm_eps, zero_init):
+        need = ctx.needs_input_grad[0]
+        out, saved = delta_packed_forward(qkvb, W, norm_eps, zero_init, save=need)
+        ctx.norm_eps = norm_eps
+        if need:
+            ctx.save_for_backward(qkvb, *saved, W)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        qkvb, v_old, v_ins, W = ctx.saved_tensors
+        gx, _ = delta_packed_backward(qkvb, (v_old, v_ins), grad_out, W, ctx.norm_eps)
+        return gx, None, None, None
+
+
+def delta_layer(qkvb, W, norm_eps=0.0, zero_init=False):
+    """See the module docstring.  qkvb: [N,H,L,3E+1] view of the slow net's rows; W: [N,H,E,E]
+    fp32 state, left holding the final fast weights (W_0 again after the backward)."""
+    return DeltaLayer.apply(qkvb, W, float(norm_eps), bool(zero_init))

@@ -11,9 +11,13 @@ the SRWM operator, so that the fused layer-level entry points can be checked aga
 * ``srwm_unroll_detached``  the learner's unroll (reinforcement_learning/torchbeast_procgen/
                      model.py:1180-1197): one step per call, the state multiplied by
                      ``notdone`` before every step and DETACHED after it (layer.py:412-421).
+* ``delta_layer``    the preparation in ``FastFFlayer.forward`` (supervised_learning/layer.py:66-96,
+                     reinforcement_learning/torchbeast/layer.py:136-176): the four-way split of
+                     the slow net's rows, sigmoid, ``elu + 1`` and the sum normalisation (with
+                     the agents' 1e-5 in the denominator, layer.py:30-33), then the delta rule.
 
-The recurrence itself is ``srwm_oracle.srwm_loop`` (pinned against the reference's own
-self test).  Parity of these two wrappers is pinned by construction only: they are the
+The recurrence itself is ``srwm_oracle.srwm_loop`` / ``delta_loop`` (pinned against the reference's own
+self test).  Parity of these wrappers is pinned by construction only: they are the
 reference layers' lines around the operator, restated; the reference has no test for them.
 
 Only ``tests/`` may import this module.
@@ -23,7 +27,7 @@ from __future__ import annotations
 import torch
 import torch.nn.functional as F
 
-from srwm_oracle import srwm_loop
+from srwm_oracle import delta_loop, srwm_loop
 
 
 def srwm_layer(x, base, shift=None, input_softmax=True):
@@ -61,3 +65,18 @@ def srwm_unroll_detached(x, base, shift, done, input_softmax=True):
         shift = [s.detach() for s in shift]
         outs.append(o)
     return torch.cat(outs, dim=2), tuple(shift)
+
+
+def delta_layer(qkvb, W0, norm_eps=0.0):
+    """qkvb [N,H,L,3E+1] raw rows (q | k | v | b); W0 [N,H,E,E].
+    layer.py:74-79 (split, sigmoid), :86-90 (elu + 1, sum normalisation), :96 (operator).
+    Returns (out [N,H,L,E], final W)."""
+    E = (qkvb.shape[-1] - 1) // 3
+    q, k, v, b = torch.split(qkvb, (E, E, E, 1), -1)
+    b = torch.sigmoid(b)
+    q = F.elu(q, 1.0, False) + 1.0
+    k = F.elu(k, 1.0, False) + 1.0
+    q = q / (q.sum(-1, keepdim=True) + norm_eps)
+    k = k / (k.sum(-1, keepdim=True) + norm_eps)
+    return delta_loop(q, k, v, b, W0)
+

@@ -332,3 +332,90 @@ def test_sr_layer_unroll_matches_the_learner_loop():
             assert float(g1[n].abs().max()) == 0.0 and float(p.grad.abs().max()) < 1e-6
         elif p.grad is not None:
             assert orc.rel_max(g1[n], p.grad) < GRAD_TOL, n
+
+
+# ---------------------------------------------------------------------------------------
+# delta rule on the packed slow-net rows
+# ---------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("E", [8, 16, 32, 64])
+@pytest.mark.parametrize("eps,zero_init", [(0.0, True), (1e-5, False)])
+def test_delta_packed_layer_parity(E, eps, zero_init):
+    from srwm_b200.layer_ops import delta_layer
+    L, B, H = 29, 3, 2
+    RS = 3 * E + 1
+    g = torch.Generator().manual_seed(300 + E)
+    raw = torch.randn(L, B, H * RS, generator=g)
+    go = torch.randn(B, H, L, E, generator=g)
+    W0 = torch.zeros(B, H, E, E) if zero_init else 0.1 * torch.randn(B, H, E, E, generator=g)
+    ro = raw.double().requires_grad_()
+    out_o, WL = lorc.delta_layer(ro.view(L, B, H, RS).permute(1, 2, 0, 3), W0.double(), eps)
+    (out_o * go.double()).sum().backward()
+
+    d = _dev()
+    rd = raw.to(d).requires_grad_()
+    W = torch.full((B, H, E, E), float("nan"), device=d) if zero_init else W0.to(d).clone()
+    out = delta_layer(rd.view(L, B, H, RS).permute(1, 2, 0, 3), W, norm_eps=eps, zero_init=zero_init)
+    res = out.transpose(1, 2).reshape(B, L, H * E).transpose(0, 1)       # layer.py:98-100 stays a view
+    assert res.data_ptr() == out.data_ptr() and res.is_contiguous()
+    assert orc.rel_max(out.detach().cpu(), out_o.detach()) < FWD_TOL
+    assert orc.rel_max(W.cpu(), WL.detach()) < FWD_TOL                    # final fast weights left in W
+    (out * go.to(d)).sum().backward()
+    assert rd.grad.shape == raw.shape and rd.grad.is_contiguous()
+    gk, go_ = rd.grad.cpu().view(L, B, H, RS), ro.grad.view(L, B, H, RS)
+    for name, sl in (("q", slice(0, E)), ("k", slice(E, 2 * E)), ("v", slice(2 * E, 3 * E)), ("b", slice(3 * E, RS))):
+        assert orc.rel_max(gk[..., sl], go_[..., sl]) < GRAD_TOL, name
+    assert float((W.cpu() - W0).abs().max()) < 1e-5                       # the backward put W_0 back
+
+
+@pytest.mark.parametrize("E", [16, 64])
+def test_delta_packed_layer_bf16_rows_at_odd_offsets(E):
+    """bf16 rows of 3E+1 values start at 2-byte offsets: staged as covering 16-byte blocks."""
+    from srwm_b200.layer_ops import delta_layer
+    L, B, H = 21, 2, 3
+    RS = 3 * E + 1
+    g = torch.Generator().manual_seed(400 + E)
+    raw = torch.randn(L, B, H * RS, generator=g).bfloat16()
+    go = torch.randn(B, H, L, E, generator=g).bfloat16()
+    ro = raw.double().requires_grad_()
+    out_o, _ = lorc.delta_layer(ro.view(L, B, H, RS).permute(1, 2, 0, 3), torch.zeros(B, H, E, E).double(), 1e-5)
+    (out_o * go.double()).sum().backward()
+    d = _dev()
+    rd = raw.to(d).requires_grad_()
+    W = torch.empty(B, H, E, E, device=d)
+    out = delta_layer(rd.view(L, B, H, RS).permute(1, 2, 0, 3), W, norm_eps=1e-5, zero_init=True)
+    assert out.dtype == torch.bfloat16
+    assert orc.rel_max(out.detach().float().cpu(), out_o.detach()) < BF16_TOL
+    (out * go.to(d)).sum().backward()
+    assert orc.rel_max(rd.grad.float().cpu(), ro.grad) < BF16_TOL
+
+
+def test_delta_packed_equals_the_layer_composition_on_gpu():
+    """Against the layers' own sequence of torch ops around the drop-in operator
+    (supervised_learning/layer.py:66-100), both on the GPU."""
+    import srwm_b200 as sb
+    from srwm_b200.layer_ops import delta_layer
+    L, B, H, E = 40, 4, 4, 32
+    RS = 3 * E + 1
+    d = _dev()
+    g = torch.Generator().manual_seed(9)
+    raw = torch.randn(L, B, H * RS, generator=g).to(d)
+    go = torch.randn(L, B, H * E, generator=g).to(d)
+    r1 = raw.clone().requires_grad_()
+    W1 = torch.empty(B, H, E, E, device=d)
+    o1 = delta_layer(r1.view(L, B, H, RS).permute(1, 2, 0, 3), W1, zero_init=True)
+    o1 = o1.transpose(1, 2).reshape(B, L, H * E).transpose(0, 1)
+    (o1 * go).sum().backward()
+    r2 = raw.clone().requires_grad_()
+    q, k, v, b = torch.split(r2.view(L, B, H, RS), (E, E, E, 1), -1)
+    b = torch.sigmoid(b)
+    q, k, v, b = (t.permute(1, 2, 0, 3) for t in (q, k, v, b))
+    q = torch.nn.functional.elu(q, 1.0, False) + 1.0
+    k = torch.nn.functional.elu(k, 1.0, False) + 1.0
+    q, k = q / q.sum(-1, keepdim=True), k / k.sum(-1, keepdim=True)
+    W2 = torch.zeros(B, H, E, E, device=d)
+    o2 = sb.fast_weight_delta(q, k, v, b, W2)
+    o2 = o2.transpose(1, 2).reshape(B, L, H * E).transpose(0, 1)
+    (o2 * go).sum().backward()
+    assert orc.rel_max(o1.detach(), o2.detach()) < FWD_TOL
+    assert orc.rel_max(r1.grad, r2.grad) < GRAD_TOL
