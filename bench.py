@@ -665,6 +665,38 @@ def run_layer_table(args):
     emit("srwm_c4_actor_layer", "SRlayer forward, L=1 B=48 H=8 d=32 hidden=256, state carried, no_grad, "
          "100 consecutive layer calls per step", actor_fused, actor_composed, {"calls": 100})
 
+    # delta-rule layer of the supervised models: L=512 B=32 H=8 d=64 (dim 512)
+    from srwm_b200.layers import FastFFlayer
+    import srwm_b200 as sb
+    F_ = torch.nn.functional
+    L_, B, H, E = 512, 32, 8, 64
+    fl = FastFFlayer(H, E, H * E, 0.0).to(device)
+    h = torch.randn(L_, B, H * E, device=device)
+    tgt = torch.randn(L_, B, H * E, device=device)
+
+    def dl_fused(_t):
+        fl.zero_grad(set_to_none=True)
+        hh = h.clone().requires_grad_()
+        (fl(hh) * tgt).sum().backward()
+
+    def dl_composed(_t):     # supervised_learning/layer.py:66-108 around the drop-in operator
+        fl.zero_grad(set_to_none=True)
+        hh = h.clone().requires_grad_()
+        qkvb = fl.slow_net(fl.layer_norm(hh)).view(L_, B, H, 3 * E + 1)
+        q, k, v, b = torch.split(qkvb, (E, E, E, 1), -1)
+        b = torch.sigmoid(b)
+        q, k, v, b = (t.permute(1, 2, 0, 3) for t in (q, k, v, b))
+        q, k = F_.elu(q, 1.0, False) + 1.0, F_.elu(k, 1.0, False) + 1.0
+        q, k = q / q.sum(-1, keepdim=True), k / k.sum(-1, keepdim=True)
+        W = torch.zeros(B, H, E, E, device=device)
+        o = sb.fast_weight_delta(q, k, v, b, W)
+        o = hh + fl.out_linear(o.transpose(1, 2).reshape(B, L_, H * E).transpose(0, 1))
+        (o * tgt).sum().backward()
+
+    emit("delta_c2_layer", "FastFFlayer fwd+bwd, L=512 B=32 H=8 d=64 dim=512, fp32: packed rows in one call vs "
+         "split / elu+1 / sum-norm / sigmoid torch ops around the operator", dl_fused, dl_composed,
+         {"tokens": L_ * B})
+
 
 def main():
     ap = argparse.ArgumentParser()

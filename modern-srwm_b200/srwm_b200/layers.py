@@ -1,14 +1,19 @@
-"""The reference's two SRWM layers on top of the fused layer-level call.
+"""The reference's SRWM and delta-rule layers on top of the fused layer-level calls.
 
 Same constructor arguments, parameter names (so a reference ``state_dict`` loads) and
 ``forward`` signatures as
 
-* ``SRWMlayer``  supervised_learning/layer.py:112-209
-* ``SRlayer``    reinforcement_learning/torchbeast/layer.py:340-421
+* ``SRWMlayer``    supervised_learning/layer.py:112-209
+* ``SRlayer``      reinforcement_learning/torchbeast/layer.py:340-421
+* ``FastFFlayer``  supervised_learning/layer.py:49-108 (``norm_eps=0``, fresh zero fast weights
+                   per call) and reinforcement_learning/torchbeast/layer.py:127-189
+                   (``FastFFlayerRL``: ``norm_eps=1e-5``, fast weights carried as state)
 
 but the per-call work around the operator -- input softmax, four ``W.repeat(bsz,1,1,1)``,
 ``shift + repeat``, the ``[L,B,H*d] -> [B,H,L,d]`` layout change and back, the four
-``W_bc - W.repeat`` subtractions -- is done inside the kernels (``layer_ops.srwm_layer``).
+``W_bc - W.repeat`` subtractions; for the delta rule the four-way split of the slow net's rows,
+``elu + 1``, the sum normalisation and the sigmoid -- is done inside the kernels
+(``layer_ops.srwm_layer`` / ``layer_ops.delta_layer``).
 ``SRlayer.unroll`` additionally runs the learner's one-step-at-a-time loop with episode
 resets (reinforcement_learning/torchbeast_procgen/model.py:1180-1197) as ONE call.
 """
@@ -19,7 +24,7 @@ import math
 import torch
 import torch.nn as nn
 
-from .layer_ops import srwm_layer
+from .layer_ops import delta_layer, srwm_layer
 
 
 def _heads(h, num_head, dim_head):
@@ -112,3 +117,43 @@ class SRlayer(nn.Module):
                                 input_softmax=True, detach_state=True)
         out = h + self.drop(self.out_linear(_merge(out)))
         return out, shift
+
+
+class FastFFlayer(nn.Module):
+    """Delta-rule fast-weight layer of the supervised-learning models: layer norm, slow net,
+    then -- in one call on the slow net's raw rows -- the q/k/beta preparation and the
+    recurrence, starting from zero fast weights."""
+
+    norm_eps = 0.0
+
+    def __init__(self, num_head, dim_head, in_dim, dropout):
+        super().__init__()
+        self.num_head, self.dim_head, self.in_dim = num_head, dim_head, in_dim
+        self.slow_net = nn.Linear(in_dim, num_head * (3 * dim_head + 1), bias=False)
+        self.layer_norm = nn.LayerNorm(in_dim)
+        self.out_linear = nn.Linear(num_head * dim_head, in_dim, bias=False)
+        self.drop = nn.Dropout(dropout)
+
+    def _rows(self, x):
+        slen, bsz, _ = x.shape
+        qkvb = self.slow_net(self.layer_norm(x))
+        return qkvb.view(slen, bsz, self.num_head, 3 * self.dim_head + 1).permute(1, 2, 0, 3)
+
+    def forward(self, x):
+        rows = self._rows(x)
+        W = torch.empty(rows.shape[0], self.num_head, self.dim_head, self.dim_head, device=x.device)
+        out = delta_layer(rows, W, norm_eps=self.norm_eps, zero_init=True)
+        return x + self.drop(self.out_linear(_merge(out)))
+
+
+class FastFFlayerRL(FastFFlayer):
+    """The agents' variant: 1e-5 in the normalisers, the fast weights are the carried state
+    (given, updated in place by the call, returned as a copy)."""
+
+    norm_eps = 1e-5
+
+    def forward(self, x, state=None):
+        assert state is not None
+        out = delta_layer(self._rows(x), state, norm_eps=self.norm_eps)
+        return x + self.drop(self.out_linear(_merge(out))), state.clone()
+

@@ -419,3 +419,46 @@ def test_delta_packed_equals_the_layer_composition_on_gpu():
     (o2 * go).sum().backward()
     assert orc.rel_max(o1.detach(), o2.detach()) < FWD_TOL
     assert orc.rel_max(r1.grad, r2.grad) < GRAD_TOL
+
+
+def test_fast_ff_layer_modules_match_composition():
+    import srwm_b200 as sb
+    from srwm_b200.layers import FastFFlayer, FastFFlayerRL
+    d = _dev()
+    torch.manual_seed(2)
+    H, E, D, L, B = 4, 16, 64, 19, 3
+    F_ = torch.nn.functional
+    for cls, eps in ((FastFFlayer, 0.0), (FastFFlayerRL, 1e-5)):
+        layer = cls(H, E, D, 0.0).to(d)
+        x = torch.randn(L, B, D, device=d)
+        tgt = torch.randn(L, B, D, device=d)
+        st0 = 0.1 * torch.randn(B, H, E, E, device=d)
+
+        layer.zero_grad()
+        x1 = x.clone().requires_grad_()
+        if cls is FastFFlayer:
+            o1, s1 = layer(x1), None
+        else:
+            o1, s1 = layer(x1, st0.clone())
+        (o1 * tgt).sum().backward()
+        g1 = [p.grad.clone() for p in layer.parameters()]
+
+        layer.zero_grad()
+        x2 = x.clone().requires_grad_()
+        qkvb = layer.slow_net(layer.layer_norm(x2)).view(L, B, H, 3 * E + 1)
+        q, k, v, b = torch.split(qkvb, (E, E, E, 1), -1)
+        b = torch.sigmoid(b)
+        q, k, v, b = (t.permute(1, 2, 0, 3) for t in (q, k, v, b))
+        q, k = F_.elu(q, 1.0, False) + 1.0, F_.elu(k, 1.0, False) + 1.0
+        q, k = q / (q.sum(-1, keepdim=True) + eps), k / (k.sum(-1, keepdim=True) + eps)
+        W = torch.zeros(B, H, E, E, device=d) if cls is FastFFlayer else st0.clone()
+        o2 = sb.fast_weight_delta(q, k, v, b, W)
+        s2 = W.clone()
+        o2 = x2 + layer.out_linear(o2.transpose(1, 2).reshape(B, L, H * E).transpose(0, 1))
+        (o2 * tgt).sum().backward()
+        assert orc.rel_max(o1.detach(), o2.detach()) < FWD_TOL
+        assert orc.rel_max(x1.grad, x2.grad) < GRAD_TOL
+        for a, p_ in zip(g1, layer.parameters()):
+            assert orc.rel_max(a, p_.grad) < GRAD_TOL
+        if s1 is not None:
+            assert orc.rel_max(s1, s2) < FWD_TOL
