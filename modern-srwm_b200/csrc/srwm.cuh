@@ -766,7 +766,17 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
   const int warp = tid / 32, lane = tid % 32;
   const int cgl = lane / NRG;
   const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
-  const int jb = cg < 4 ? cg : -1;   // column groups 0..3 (warp 0 when NRG <= 8) own w_b columns 0..3
+  // The E x 4 block w_b and its gradient.  WBREG: every warp owns 4/NWARP of the four columns and
+  // every lane one row pair of one column, in registers -- the work and the row reduction are
+  // spread evenly over the block (left to the column groups 0..3, i.e. to warp 0, it put a
+  // tenth more instructions on the one warp the step's barrier then waits for).  Otherwise the
+  // columns live transposed in shared memory and column groups 0..3 handle one each.
+  constexpr int CPW = NWARP <= 4 ? 4 / NWARP : 0;
+  constexpr bool WBREG = (NWARP <= 4) && (CGW == CPW * R2);
+  const int wi2 = cgl % R2;                                   // WBREG: row pair of this lane
+  const int wrow = row_of<R, NRG>(rg, 2 * wi2);               // its first row (the second is wrow + 1)
+  const int jb = WBREG ? warp * CPW + cgl / R2 : (cg < 4 ? cg : -1);
+  float wbr[2] = {0.f, 0.f}, gbr[2] = {0.f, 0.f};
 
   extern __shared__ __align__(16) unsigned char smem[];
   unsigned char* s_o = smem + 2 * SM::IN_BYTES;
@@ -808,9 +818,18 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
   {
     const float* ggwb = p.gwb.mat(n, h);
     const float* bb = has_base ? p.bwb.mat(n, h) : nullptr;
-    for (int i = tid; i < 4 * E; i += P) {
-      wbT[(i % 4) * E + i / 4] = gwb[i] + (bb ? bb[i] : 0.f);
-      gbT[(i % 4) * E + i / 4] = gin ? ggwb[i] : 0.f;
+    if constexpr (WBREG) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = (wrow + u) * 4 + jb;
+        wbr[u] = gwb[i] + (bb ? bb[i] : 0.f);
+        gbr[u] = gin ? ggwb[i] : 0.f;
+      }
+    } else {
+      for (int i = tid; i < 4 * E; i += P) {
+        wbT[(i % 4) * E + i / 4] = gwb[i] + (bb ? bb[i] : 0.f);
+        gbT[(i % 4) * E + i / 4] = gin ? ggwb[i] : 0.f;
+      }
     }
   }
 
@@ -911,7 +930,25 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       for (int i2 = 0; i2 < R2; ++i2) unpack2(gkr2[i2], gkr[2 * i2], gkr[2 * i2 + 1]);
       // w_b column jb: same three operations on shared-memory state
       float rb = 0.f, bdj = 0.f;
-      if (jb >= 0) {
+      if constexpr (WBREG) {
+        float kp0 = 0.f, kp1 = 0.f;
+#pragma unroll
+        for (int i2 = 0; i2 < R2; ++i2)
+          if (i2 == wi2) unpack2(k2[i2], kp0, kp1);
+        bdj = sbd[t * 4 + jb];
+        const float insb = beta[3] * bdj;
+        wbr[0] = fmaf(-kp0, insb, wbr[0]);
+        wbr[1] = fmaf(-kp1, insb, wbr[1]);
+        rb = fmaf(kp1, gbr[1], kp0 * gbr[0]);
+#pragma unroll
+        for (int i2 = 0; i2 < R2; ++i2)
+          if (i2 == wi2) {
+            gkr[2 * i2] = fmaf(-gbr[0], insb, gkr[2 * i2]);
+            gkr[2 * i2 + 1] = fmaf(-gbr[1], insb, gkr[2 * i2 + 1]);
+          }
+#pragma unroll
+        for (int off = 1; off < NRG * R2; off <<= 1) rb += __shfl_xor_sync(0xffffffffu, rb, off);   // all rows of the column
+      } else if (jb >= 0) {
         float kr[R], wr[R], gr[R];
         ld_rows<R, NRG>(sk + t * E, rg, kr);
         ld_rows<R, NRG>(wbT + jb * E, rg, wr);
@@ -939,7 +976,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         for (int z = 0; z < 3; ++z)
 #pragma unroll
           for (int j = 0; j < C; ++j) v[z * C + j] = rcol[z][j];
-        v[3 * C] = rb;
+        if constexpr (!WBREG) v[3 * C] = rb;   // (WBREG: the column sum of w_b is already complete)
         reduce_scatter<PADN, NRG, 1>(v, lane);
         const int g0 = rg * S_COL;
         const int zl = min(g0 / C, 3);                     // block of this lane's values (3: the w_b column)
@@ -962,7 +999,12 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
 #pragma unroll
           for (int j = 0; j < C; ++j)
             rcol[z][j] = __shfl_sync(0xffffffffu, fin[(z * C + j) % S_COL], base + (z * C + j) / S_COL);   // now gd
-        gdb = __shfl_sync(0xffffffffu, fin[(3 * C) % S_COL], base + (3 * C) / S_COL);
+        if constexpr (WBREG) {
+          gdb = beta[3] * rb;
+          sc8[3] += (rg == 0 && wi2 == 0) ? rb * bdj : 0.f;
+        } else {
+          gdb = __shfl_sync(0xffffffffu, fin[(3 * C) % S_COL], base + (3 * C) / S_COL);
+        }
       } else {
 #pragma unroll
         for (int z = 0; z < 3; ++z) {
@@ -975,10 +1017,12 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
             rcol[z][j] = beta[z] * r;   // now gd
           }
         }
-        rb = allreduce_rows<NRG>(rb);
+        if constexpr (!WBREG) rb = allreduce_rows<NRG>(rb);
         gdb = beta[3] * rb;
         sc8[3] = rb * bdj;
         if (rg != 0) { sc8[0] = 0.f; sc8[1] = 0.f; sc8[2] = 0.f; sc8[3] = 0.f; }   // count each column once
+        if constexpr (WBREG)
+          if (wi2 != 0) sc8[3] = 0.f;
       }
       // G += (q-k)^T gd ; u = W(t-1) gd (row partial)
       u64 d2[R2], u2[R2];
@@ -1008,7 +1052,18 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       blk2(Wk, Gk, rcol[2]);
 #pragma unroll
       for (int i2 = 0; i2 < R2; ++i2) unpack2(u2[i2], ur[2 * i2], ur[2 * i2 + 1]);
-      if (jb >= 0) {
+      if constexpr (WBREG) {
+#pragma unroll
+        for (int i2 = 0; i2 < R2; ++i2)
+          if (i2 == wi2) {
+            float da, db;
+            unpack2(d2[i2], da, db);
+            gbr[0] = fmaf(da, gdb, gbr[0]);
+            gbr[1] = fmaf(db, gdb, gbr[1]);
+            ur[2 * i2] = fmaf(wbr[0], gdb, ur[2 * i2]);
+            ur[2 * i2 + 1] = fmaf(wbr[1], gdb, ur[2 * i2 + 1]);
+          }
+      } else if (jb >= 0) {
         float wr[R], gr[R];
         ld_rows<R, NRG>(wbT + jb * E, rg, wr);
         ld_rows<R, NRG>(gbT + jb * E, rg, gr);
@@ -1130,7 +1185,18 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
       float gxr[R];
 #pragma unroll
       for (int i2 = 0; i2 < R2; ++i2) unpack2(gx2[i2], gxr[2 * i2], gxr[2 * i2 + 1]);
-      if (jb >= 0) {
+      if constexpr (WBREG) {
+        const float b = sbeta[t * 4 + jb];
+        const float pb = sc[0] * b * (1.f - b);
+#pragma unroll
+        for (int i2 = 0; i2 < R2; ++i2)
+          if (i2 == wi2) {
+            gxr[2 * i2] = fmaf(wbr[0], pb, gxr[2 * i2]);
+            gxr[2 * i2 + 1] = fmaf(wbr[1], pb, gxr[2 * i2 + 1]);
+            gbr[0] = fmaf(xr[2 * i2], pb, gbr[0]);
+            gbr[1] = fmaf(xr[2 * i2 + 1], pb, gbr[1]);
+          }
+      } else if (jb >= 0) {
         float wr[R], gr[R];
         ld_rows<R, NRG>(wbT + jb * E, rg, wr);
         ld_rows<R, NRG>(gbT + jb * E, rg, gr);
@@ -1194,9 +1260,18 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
   {
     float* ggwb = p.gwb.mat(n, h);
     const float* bb = has_base ? p.bwb.mat(n, h) : nullptr;
-    for (int i = tid; i < 4 * E; i += P) {
-      ggwb[i] = gbT[(i % 4) * E + i / 4];
-      if (restore) gwb[i] = wbT[(i % 4) * E + i / 4] - (bb ? bb[i] : 0.f);
+    if constexpr (WBREG) {
+#pragma unroll
+      for (int u = 0; u < 2; ++u) {
+        const int i = (wrow + u) * 4 + jb;
+        ggwb[i] = gbr[u];
+        if (restore) gwb[i] = wbr[u] - (bb ? bb[i] : 0.f);
+      }
+    } else {
+      for (int i = tid; i < 4 * E; i += P) {
+        ggwb[i] = gbT[(i % 4) * E + i / 4];
+        if (restore) gwb[i] = wbT[(i % 4) * E + i / 4] - (bb ? bb[i] : 0.f);
+      }
     }
   }
 }
