@@ -515,7 +515,7 @@ def run_ours(args):
 # divided by sequences x steps; profiles/*_d64_bf16_*.txt).  `roofline.traffic` scales this
 # to a full launch by the sequence-steps it processes (traffic is streamed once, so it
 # grows in proportion).
-NCU_BWD_DRAM_BYTES_PER_SEQ_STEP = {"srwm": 1841.0, "delta": 1423.7}
+NCU_BWD_DRAM_BYTES_PER_SEQ_STEP = {"srwm": 1850.2, "delta": 1423.7}
 
 
 def run_table(args):
@@ -698,6 +698,73 @@ def run_layer_table(args):
          {"tokens": L_ * B})
 
 
+def run_layer_prof(args):
+    """The layer-level kernels on a capture-sized workload (activations > L2, a whole number of
+    waves), for profiler runs: `srwm` = layer forward (input softmax, un-repeated slow weights,
+    shift state, reset mask) + detached-state backward, B=37 H=16 L=512 d=64 bf16; `delta` =
+    packed forward + packed backward, B=74 H=16 L=1024 d=64 bf16.  One JSON line with the
+    CUDA-event time of each kernel and its algorithmic bytes."""
+    from srwm_b200 import layer_ops as lo
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    g = torch.Generator(device=device).manual_seed(5)
+    H, E = 16, 64
+    hbm_peak, peak_kind, _ = load_peaks()
+    if args.layer_prof == "srwm":
+        B, L_ = 37, 512
+        x = OpBench._big_randn((B, H, L_, E), g, torch.bfloat16)
+        go = OpBench._big_randn((B, H, L_, E), g, torch.bfloat16)
+        std = E ** -0.5
+        base = [torch.randn(1, H, E, E, device=device, generator=g) * std for _ in range(3)]
+        base.append(torch.randn(1, H, E, 4, device=device, generator=g) * std)
+        shift = [0.05 * std * torch.randn(B, H, E, w.shape[-1], device=device, generator=g) for w in base]
+        done = torch.rand(B, L_, device=device, generator=g) < 0.01
+        names = ("srwm_fwd_col_kernel<EXT>", "srwm_bwd_det_kernel")
+        fbytes = B * H * (L_ * (2 * E * 2 + (5 * E + 8) * 4) + 3 * E * (3 * E + 4) * 4)
+        bbytes = B * H * (L_ * (3 * E * 2 + (2 * E + 4) * 4) + 3 * E * E * 4)
+
+        def fwd():
+            return lo.srwm_layer_forward(x, base, shift, done, True)
+
+        def bwd(res):
+            return lo.srwm_backward_detached(x, res[2], go, base[0], shift[0], done, True)
+    else:
+        B, L_ = 74, 1024
+        RS = 3 * E + 1
+        raw = OpBench._big_randn((L_, B, H * RS), g, torch.bfloat16)
+        rows = raw.view(L_, B, H, RS).permute(1, 2, 0, 3)
+        go = OpBench._big_randn((B, H, L_, E), g, torch.bfloat16)
+        W = torch.empty(B, H, E, E, device=device)
+        names = ("delta_fwd_kernel<PACKED>", "delta_bwd_kernel<PACKED>")
+        fbytes = B * H * (L_ * (RS * 2 + E * 2 + 2 * E * 4) + E * E * 4)
+        bbytes = B * H * (L_ * (2 * RS * 2 + E * 2 + 2 * E * 4) + 2 * E * E * 4)
+
+        def fwd():
+            return lo.delta_packed_forward(rows, W, 0.0, True)
+
+        def bwd(res):
+            return lo.delta_packed_backward(rows, res[1], go, W, 0.0)
+    tf, tb = [], []
+    for i in range(args.warmup + args.steps):
+        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        e[0].record()
+        res = fwd()
+        e[1].record()
+        bwd(res)
+        e[2].record()
+        torch.cuda.synchronize(device)
+        if i >= args.warmup:
+            tf.append(e[0].elapsed_time(e[1]))
+            tb.append(e[1].elapsed_time(e[2]))
+    f, b = sum(tf) / len(tf), sum(tb) / len(tb)
+    print(json.dumps({"workload": f"{args.layer_prof}_layer_prof", "sequences": B * H, "steps_per_sequence": L_,
+                      "kernels": {names[0]: {"ms": f, "algorithmic_bytes": fbytes, "GB/s": fbytes / f / 1e6,
+                                             "frac_of_hbm_peak": fbytes / f / 1e6 / hbm_peak},
+                                  names[1]: {"ms": b, "algorithmic_bytes": bbytes, "GB/s": bbytes / b / 1e6,
+                                             "frac_of_hbm_peak": bbytes / b / 1e6 / hbm_peak}},
+                      "peak_source": f"of {peak_kind}"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -712,8 +779,12 @@ def main():
     ap.add_argument("--table", action="store_true", help="operator-level timings of every configuration")
     ap.add_argument("--layer-table", action="store_true",
                     help="layer-level timings: fused layer call vs torch ops around the operator")
+    ap.add_argument("--layer-prof", choices=["srwm", "delta"], default=None,
+                    help="layer-level kernels on a capture-sized workload (for profiler runs)")
     args = ap.parse_args()
-    if args.layer_table:
+    if args.layer_prof:
+        run_layer_prof(args)
+    elif args.layer_table:
         run_layer_table(args)
     elif args.table:
         run_table(args)
