@@ -17,7 +17,10 @@ constexpr unsigned EXT_FLAGS = F_INPUT_SOFTMAX | F_BASE;
 
 template <int E, int V, int P, int R, int T, bool PK, int MINB>
 int run(const SrwmBwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
-  if (p.flags & EXT_FLAGS) {
+  // (at E = 64 the EXT instantiation also serves plain calls: it reads x as fp32 rows converted once
+  // per chunk, which leaves the step loop fewer conversions and fewer spilled registers; measured
+  // 5 % faster with bf16 streams, equal with fp32 streams)
+  if ((p.flags & EXT_FLAGS) || (E == 64 && V == 0)) {
     if constexpr (V == 0) {
       constexpr int smem = SrwmBwdSmem<TIO, E, P, T, true>::TOTAL;
       if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; }

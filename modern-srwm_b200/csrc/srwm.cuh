@@ -213,12 +213,14 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
         sxs = d;
       }
     }
+    // reset flags of the chunk as a bit mask (one ballot per chunk instead of a load per step)
+    const unsigned dmask = has_done ? __ballot_sync(0xffffffffu, (tid % 32) < nt && sdone[tid % 32] != 0) : 0u;
 
     #pragma unroll 1
 
     for (int t = 0; t < nt; ++t, par ^= 1) {
       if constexpr (EXT) {
-        if (has_done && sdone[t]) {   // episode boundary: the shift goes back to zero
+        if ((dmask >> t) & 1u) {   // episode boundary: the shift goes back to zero
           load_tile<E, C, R, NRG>(p.bWy.mat(n, h), rg, cg, Wy);
           load_tile<E, C, R, NRG>(p.bWq.mat(n, h), rg, cg, Wq);
           load_tile<E, C, R, NRG>(p.bWk.mat(n, h), rg, cg, Wk);
@@ -418,6 +420,7 @@ struct SrwmFwdColSmem {
 template <typename TIO, int E, int T, bool PK, int MINB, bool DPRE, int NRP, bool EXT = false>
 __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdParams p) {
   static_assert(E == 16 || E == 32 || E == 64, "column layout: one warp per block");
+  static_assert(T <= 32, "reset flags of a chunk travel as one 32-bit mask");
   // Lane (cq, rp) of a warp holds CPL adjacent columns x RL rows (row part rp of NRP) of the
   // warp's block.  NRP = 1 is the pure column layout; NRP > 1 trades a log2(NRP)-stage
   // shuffle per pass for 1/NRP of the broadcast operand loads (the shared-memory data pipe
@@ -536,12 +539,14 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       __syncthreads();
       sxf = xf32;
     }
+    // reset flags of the chunk as a bit mask (one ballot per chunk instead of a load per step)
+    const unsigned dmask = has_done ? __ballot_sync(0xffffffffu, lane < nt && sdone[lane] != 0) : 0u;
 
     #pragma unroll 1
 
     for (int t = 0; t < nt; ++t, par ^= 1) {
       if constexpr (EXT) {
-        if (has_done && sdone[t]) {   // episode boundary: the shift goes back to zero
+        if ((dmask >> t) & 1u) {   // episode boundary: the shift goes back to zero
           load_state(gB, nullptr);
           if (warp == 0) {
             const float* bb = p.bwb.mat(n, h);
@@ -1383,9 +1388,10 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_det_kernel(const SrwmBwdDetP
       sxs = xf32;
     }
 
+    const unsigned dmask = has_done ? __ballot_sync(0xffffffffu, lane < nt && sdone[lane] != 0) : 0u;
 #pragma unroll 1
     for (int t = 0; t < nt; ++t) {
-      if (has_done && sdone[t]) load_tile<E, C, R, NRG>(gB, rg, cg, W);
+      if ((dmask >> t) & 1u) load_tile<E, C, R, NRG>(gB, rg, cg, W);
       float xr[R], kr[R], g[C], dz[C];
       ld_rows<R, NRG>(sxs + t * E, rg, xr);
       ld_rows<R, NRG>(sk + t * E, rg, kr);
