@@ -110,8 +110,7 @@ struct DeltaFwdSmem {
   static constexpr int RSB = (3 * E + 1) * (int)sizeof(TIO);     // bytes of a packed row
   static constexpr int PK_PITCH = ((RSB + 30) / 16) * 16;        // the 16-byte blocks that can cover it
   static constexpr int IN_BYTES = PACKED ? T * PK_PITCH : 3 * T * ROW_IO + BETA_BYTES;   // one staging buffer
-  // prepared q,k,v,beta (fp32); plain calls with 16-bit streams convert q,k,v to fp32 once per chunk
-  static constexpr int DENSE_BYTES = PACKED ? 3 * T * ROW_F + BETA_BYTES : (sizeof(TIO) == 2 ? 3 * T * ROW_F : 0);
+  static constexpr int DENSE_BYTES = PACKED ? 3 * T * ROW_F + BETA_BYTES : 0;   // prepared q,k,v,beta (fp32)
   static constexpr int OUT_BYTES = T * ROW_IO + 2 * T * ROW_F;   // out, v_old, v_ins
   static constexpr int TOTAL = 2 * IN_BYTES + DENSE_BYTES + OUT_BYTES;
 };
@@ -120,8 +119,7 @@ template <typename TIO, int E, int P, int R, int T, bool PK, int MINB, bool PACK
 __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams p) {
   using TL = Tiling<E, P, R>;
   using SM = DeltaFwdSmem<TIO, E, T, PACKED>;
-  constexpr bool CONV = !PACKED && sizeof(TIO) == 2;   // 16-bit streams: converted to fp32 once per chunk
-  using TS = typename std::conditional<PACKED || CONV, float, TIO>::type;   // what the step loop reads
+  using TS = typename std::conditional<PACKED, float, TIO>::type;   // element type the step loop reads
   constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2;
   const int tid = threadIdx.x;
   const int rg = tid % NRG, cg = tid / NRG;
@@ -205,13 +203,6 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
                                                       dq + 2 * T * E, dq + 3 * T * E, nullptr, nullptr, nt, tid);
       __syncthreads();
       sq = dq; sk = dq + T * E; sv = dq + 2 * T * E; sb = dq + 3 * T * E;
-    } else if constexpr (CONV) {
-      convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib), dense, nt, tid);
-      convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO), dense + T * E, nt, tid);
-      convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib + 2 * T * SM::ROW_IO), dense + 2 * T * E, nt, tid);
-      __syncthreads();
-      sq = dense; sk = dense + T * E; sv = dense + 2 * T * E;
-      sb = beta_buf(c & 1);
     } else {
       sq = reinterpret_cast<const TS*>(ib);
       sk = reinterpret_cast<const TS*>(ib + T * SM::ROW_IO);
@@ -318,8 +309,7 @@ struct DeltaBwdSmem {
   // q,k,v (io, or the packed rows) | gout (io) | v_old, v_ins (f32) | beta
   static constexpr int QKV_BYTES = PACKED ? T * PK_PITCH : 3 * T * ROW_IO;
   static constexpr int IN_BYTES = QKV_BYTES + T * ROW_IO + 2 * T * ROW_F + (PACKED ? 0 : BETA_BYTES);
-  // q,k,v | beta, sum_q, sum_k ; plain calls with 16-bit streams convert q,k,v to fp32 once per chunk
-  static constexpr int DENSE_BYTES = PACKED ? 3 * T * ROW_F + 3 * BETA_BYTES : (sizeof(TIO) == 2 ? 3 * T * ROW_F : 0);
+  static constexpr int DENSE_BYTES = PACKED ? 3 * T * ROW_F + 3 * BETA_BYTES : 0;   // q,k,v | beta, sum_q, sum_k
   static constexpr int GV_BYTES = T * ROW_IO;
   static constexpr int PART_BYTES = T * NWARP * 2 * ROW_F;       // per-warp partial gq, gk
   static constexpr int GB_BYTES = ((T * NWARP * 4 + 15) / 16) * 16;
@@ -330,8 +320,7 @@ template <typename TIO, int E, int P, int R, int T, bool PK, int MINB, bool PACK
 __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams p) {
   using TL = Tiling<E, P, R>;
   using SM = DeltaBwdSmem<TIO, E, P, T, PACKED>;
-  constexpr bool CONV = !PACKED && sizeof(TIO) == 2;
-  using TS = typename std::conditional<PACKED || CONV, float, TIO>::type;
+  using TS = typename std::conditional<PACKED, float, TIO>::type;
   constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2, NWARP = TL::NWARP, CGW = TL::CGW;
   // row sums leave the warp through a reduce-scatter when the tile shape allows it
   constexpr bool SCATTER = (CGW >= 2) && ((2 * R) % CGW == 0) && ((2 * R) / CGW <= 4 || ((2 * R) / CGW) % 4 == 0);
@@ -423,13 +412,6 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
                                                       dq + 2 * T * E, dq + 3 * T * E, dsq, dsk, nt, tid);
       __syncthreads();
       sq = dq; sk = dq + T * E; sv = dq + 2 * T * E; sb = dq + 3 * T * E;
-    } else if constexpr (CONV) {
-      convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib), dense, nt, tid);
-      convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO), dense + T * E, nt, tid);
-      convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib + 2 * T * SM::ROW_IO), dense + 2 * T * E, nt, tid);
-      __syncthreads();
-      sq = dense; sk = dense + T * E; sv = dense + 2 * T * E;
-      sb = beta_buf(c & 1);
     } else {
       sq = reinterpret_cast<const TS*>(ib);
       sk = reinterpret_cast<const TS*>(ib + T * SM::ROW_IO);
