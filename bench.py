@@ -665,6 +665,96 @@ def run_layer_table(args):
     emit("srwm_c4_actor_layer", "SRlayer forward, L=1 B=48 H=8 d=32 hidden=256, state carried, no_grad, "
          "100 consecutive layer calls per step", actor_fused, actor_composed, {"calls": 100})
 
+    # ---- model-level: the C3 / C4 stacks (SRWM layer + feed-forward block, twice) -----------------
+    import torch.nn as nn
+
+    class FF(nn.Module):   # the residual feed-forward block between the fast-weight layers
+        def __init__(self, ff_dim, dim):
+            super().__init__()
+            self.norm = nn.LayerNorm(dim)
+            self.net = nn.Sequential(nn.Linear(dim, ff_dim), nn.ReLU(), nn.Linear(ff_dim, dim))
+
+        def forward(self, x):
+            return self.net(self.norm(x)) + x
+
+    # C3: tokens [L=128, B=128, 512] + one-hot(5) -> Linear(517,512) -> 2 x (SRWMlayer(16,32,512) + FF(2048))
+    #     -> Linear(512,5), cross-entropy at every position
+    L_, B, H, E, D = 128, 128, 16, 32, 512
+    c3 = nn.ModuleDict(dict(inp=nn.Linear(D + 5, D), out=nn.Linear(D, 5),
+                            sr=nn.ModuleList([SRWMlayer(H, E, D, 0.0) for _ in range(2)]),
+                            ff=nn.ModuleList([FF(2048, D) for _ in range(2)]))).to(device)
+    feats = torch.randn(L_, B, D, device=device)
+    onehot = torch.nn.functional.one_hot(torch.randint(0, 5, (L_, B), device=device), 5).float()
+    tok = torch.cat([feats, onehot], -1)
+    labels = torch.randint(0, 5, (L_ * B,), device=device)
+
+    def c3_step(fused):
+        c3.zero_grad(set_to_none=True)
+        hcur = c3["inp"](tok)
+        for sr, ff in zip(c3["sr"], c3["ff"]):
+            hcur = sr(hcur) if fused else composed_sr_layer(sr, hcur, None, always_softmax=False)[0]
+            hcur = ff(hcur)
+        torch.nn.functional.cross_entropy(c3["out"](hcur).view(L_ * B, 5), labels).backward()
+
+    emit("srwm_c3_model", "2 x (SRWMlayer(16 heads, d=32, dim 512) + FF(2048)) between Linear(517,512) and "
+         "Linear(512,5), cross-entropy, L=128 B=128 fp32, forward+backward", lambda _t: c3_step(True),
+         lambda _t: c3_step(False), {"tokens": L_ * B})
+
+    # C4: Linear(257,256) -> 2 x (SRlayer(8 heads, d=32) + FF(512)); learner unroll T=100 B=32 with done
+    T, B, H, E, D = 100, 32, 8, 32, 256
+    c4 = nn.ModuleDict(dict(inp=nn.Linear(D + 1, D), sr=nn.ModuleList([SRlayer(H, E, D, 0.0) for _ in range(2)]),
+                            ff=nn.ModuleList([FF(512, D) for _ in range(2)]))).to(device)
+    obs = torch.randn(T, B, D + 1, device=device)
+    tgt4 = torch.randn(T, B, D, device=device)
+    done4 = torch.rand(T, B, device=device) < 0.01
+
+    def fresh_state(bsz):
+        return [[0.05 * torch.randn(bsz, H, E, E, device=device) for _ in range(3)] +
+                [0.05 * torch.randn(bsz, H, E, 4, device=device)] for _ in range(2)]
+
+    st4 = fresh_state(B)
+
+    def c4_fused(_t):      # layer by layer over the whole unroll (a layer's state depends on its own inputs only)
+        c4.zero_grad(set_to_none=True)
+        hcur = c4["inp"](obs)
+        for i, (sr, ff) in enumerate(zip(c4["sr"], c4["ff"])):
+            hcur, _ = sr.unroll(hcur, done4, st4[i])
+            hcur = ff(hcur)
+        (hcur * tgt4).sum().backward()
+
+    def c4_composed(_t):   # step by step, as the learner does (torchbeast_procgen/model.py:1180-1197)
+        c4.zero_grad(set_to_none=True)
+        st = [list(s) for s in st4]
+        outs = []
+        for t in range(T):
+            nd = (~done4[t]).float().view(B, 1, 1, 1)
+            hcur = c4["inp"](obs[t:t + 1])
+            for i, (sr, ff) in enumerate(zip(c4["sr"], c4["ff"])):
+                hcur, st[i] = composed_sr_layer(sr, hcur, [nd * w for w in st[i]])
+                hcur = ff(hcur)
+            outs.append(hcur)
+        (torch.cat(outs, 0) * tgt4).sum().backward()
+
+    emit("srwm_c4_model_learner", "Linear(257,256) + 2 x (SRlayer(8 heads, d=32) + FF(512)), learner unroll T=100 B=32 "
+         "with done mask, forward+backward: layer-wise fused unroll vs the step-by-step loop", c4_fused, c4_composed,
+         {"env_steps": T * B})
+
+    Ba = 48
+    obs_a = torch.randn(1, Ba, D + 1, device=device)
+    sta4 = fresh_state(Ba)
+
+    def c4_actor(fused):
+        st = [list(s) for s in sta4]
+        with torch.no_grad():
+            for _ in range(100):
+                hcur = c4["inp"](obs_a)
+                for i, (sr, ff) in enumerate(zip(c4["sr"], c4["ff"])):
+                    hcur, st[i] = sr(hcur, st[i]) if fused else composed_sr_layer(sr, hcur, st[i])
+                    hcur = ff(hcur)
+
+    emit("srwm_c4_model_actor", "same stack, actor: one step, B=48, state carried, no_grad, 100 consecutive steps",
+         lambda _t: c4_actor(True), lambda _t: c4_actor(False), {"calls": 100})
+
     # delta-rule layer of the supervised models: L=512 B=32 H=8 d=64 (dim 512)
     from srwm_b200.layers import FastFFlayer
     import srwm_b200 as sb
