@@ -289,6 +289,12 @@ def _reduce_to(g, shape):
 def srwm_layer(x, W_y, W_q, W_k, w_b, shift=None, done=None, input_softmax=True, detach_state=False):
     """See the module docstring.  Returns (out, (shift_W_y, shift_W_q, shift_W_k, shift_w_b))."""
     s = (None, None, None, None) if shift is None else tuple(shift)
+    if not (torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (x, W_y, W_q, W_k, w_b, *s))):
+        # nothing to differentiate (the actors' path): skip the autograd machinery altogether
+        if done is not None and not detach_state:
+            raise ValueError("done (in-kernel state reset) needs detach_state=True")
+        out, shift_out, _ = srwm_layer_forward(x, (W_y, W_q, W_k, w_b), shift, done, input_softmax, save=False)
+        return out, tuple(shift_out)
     res = SrwmLayer.apply(x, W_y, W_q, W_k, w_b, *s, done, bool(input_softmax), bool(detach_state))
     return res[0], tuple(res[1:])
 

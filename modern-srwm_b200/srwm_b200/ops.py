@@ -403,6 +403,27 @@ class DeltaFastWeight(torch.autograd.Function):
         return gQ.to(Q.dtype), gK.to(K.dtype), gV.to(V.dtype), gB.to(beta.dtype), None
 
 
-self_ref_v0 = SelfRefv0.apply
-stateful_self_ref_v0 = StatefulSelfRefv0.apply
-fast_weight_delta = DeltaFastWeight.apply
+def _no_grad_needed(*ts):
+    return not (torch.is_grad_enabled() and any(t.requires_grad for t in ts))
+
+
+def self_ref_v0(x, W_y, W_q, W_k, w_b):
+    """``SelfRefv0.apply`` (supervised_learning/self_ref_v0/__init__.py:216); when nothing needs a
+    gradient (the actors' single-step calls) the autograd machinery is skipped."""
+    if _no_grad_needed(x, W_y, W_q, W_k, w_b):
+        return srwm_forward(x, W_y, W_q, W_k, w_b, save=False)[0]
+    return SelfRefv0.apply(x, W_y, W_q, W_k, w_b)
+
+
+def stateful_self_ref_v0(x, W_y, W_q, W_k, w_b):
+    """``StatefulSelfRefv0.apply`` (supervised_learning/self_ref_v0/__init__.py:217)."""
+    if _no_grad_needed(x, W_y, W_q, W_k, w_b):
+        return (srwm_forward(x, W_y, W_q, W_k, w_b, save=False)[0], W_y, W_q, W_k, w_b)
+    return StatefulSelfRefv0.apply(x, W_y, W_q, W_k, w_b)
+
+
+def fast_weight_delta(Q, K, V, beta, W):
+    """``DeltaFastWeight.apply`` (supervised_learning/fast_weight/__init__.py:100)."""
+    if _no_grad_needed(Q, K, V, beta):
+        return delta_forward(Q, K, V, beta, W, save=False)[0]
+    return DeltaFastWeight.apply(Q, K, V, beta, W)
