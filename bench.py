@@ -752,8 +752,18 @@ def run_layer_table(args):
                     hcur, st[i] = sr(hcur, st[i]) if fused else composed_sr_layer(sr, hcur, st[i])
                     hcur = ff(hcur)
 
+    from srwm_b200.graphs import GraphedSRStep
+    gstep = GraphedSRStep(list(zip(c4["sr"], c4["ff"])), sta4, obs_a, pre=c4["inp"])
+
+    def c4_actor_graphed(_t):
+        for _ in range(100):
+            gstep(obs_a)
+
+    ms_g = timed_region(c4_actor_graphed, args.steps, args.warmup, False, device)
     emit("srwm_c4_model_actor", "same stack, actor: one step, B=48, state carried, no_grad, 100 consecutive steps",
-         lambda _t: c4_actor(True), lambda _t: c4_actor(False), {"calls": 100})
+         lambda _t: c4_actor(True), lambda _t: c4_actor(False),
+         {"calls": 100, "graphed_ms": ms_g, "graphed_us_per_step": ms_g * 10.0,
+          "graphed_env_steps_per_s": 100 * Ba / (ms_g * 1e-3)})
 
     # delta-rule layer of the supervised models: L=512 B=32 H=8 d=64 (dim 512)
     from srwm_b200.layers import FastFFlayer

@@ -77,10 +77,13 @@ def _done_bytes(done, N, Ln):
     return (done != 0).view(torch.uint8)
 
 
-def srwm_layer_forward(x, base, shift=None, done=None, input_softmax=True, save=True):
+def srwm_layer_forward(x, base, shift=None, done=None, input_softmax=True, save=True, inplace_state=False):
     """Forward.  x [N,H,L,E] (raw activations with ``input_softmax``), base = 4 slow-weight
     tensors [1,H,E,.] (or per sample [N,H,E,.]), shift = optional 4 tensors [N,H,E,.], done =
-    optional [N,L].  Returns (out, shift_out (4 new tensors), saved or None)."""
+    optional [N,L].  Returns (out, shift_out (4 new tensors), saved or None).
+    ``inplace_state``: write the new shift over the given one (inference only: every thread
+    overwrites exactly the state elements it read at the start, but a backward would no longer
+    find its initial shift)."""
     _require_cuda(x, *base)
     N, H, Ln, E = x.shape
     shapes = [(E, E)] * 3 + [(E, 4)]
@@ -97,7 +100,11 @@ def srwm_layer_forward(x, base, shift=None, done=None, input_softmax=True, save=
         shift = [_dense_state(s.detach()) for s in shift]
     done_b = _done_bytes(done, N, Ln)
     out = _like(xs)
-    shift_out = [torch.empty((N, H) + s, device=dev, dtype=torch.float32) for s in shapes]
+    if inplace_state:
+        assert shift is not None and not save, "in-place state update is for inference calls with a carried state"
+        shift_out = shift
+    else:
+        shift_out = [torch.empty((N, H) + s, device=dev, dtype=torch.float32) for s in shapes]
     a = L.SrwmFwdArgs()
     a.N, a.H, a.L, a.E = N, H, Ln, E
     a.io_dtype = dt
@@ -116,8 +123,9 @@ def srwm_layer_forward(x, base, shift=None, done=None, input_softmax=True, save=
     else:
         a.q = a.k = a.beta = a.y_diff = a.q_diff = a.k_diff = a.beta_diff = _NULL_SEQ
     if Ln == 0:      # nothing to run: the state is carried through unchanged
-        for so, si in zip(shift_out, shift if shift is not None else [None] * 4):
-            so.zero_() if si is None else so.copy_(si)
+        if not inplace_state:
+            for so, si in zip(shift_out, shift if shift is not None else [None] * 4):
+                so.zero_() if si is None else so.copy_(si)
         return out, shift_out, saved
     e = _ext(base, shift, done_b)
     with torch.cuda.device(dev):

@@ -462,3 +462,38 @@ def test_fast_ff_layer_modules_match_composition():
             assert orc.rel_max(a, p_.grad) < GRAD_TOL
         if s1 is not None:
             assert orc.rel_max(s1, s2) < FWD_TOL
+
+
+def test_graphed_actor_step_matches_eager():
+    """The CUDA-graph replay of an actor step (two SRlayer + feed-forward blocks, state updated in
+    place) against the same stack called eagerly, over several steps with a reset in between."""
+    import torch.nn as nn
+    from srwm_b200.graphs import GraphedSRStep
+    from srwm_b200.layers import SRlayer
+    d = _dev()
+    torch.manual_seed(4)
+    H, E, D, B = 8, 32, 256, 12
+    layers = [(SRlayer(H, E, D, 0.0).to(d), nn.Sequential(nn.LayerNorm(D), nn.Linear(D, D)).to(d)) for _ in range(2)]
+    pre = nn.Linear(D + 1, D).to(d)
+    st0 = [[0.05 * torch.randn(B, H, E, E, device=d) for _ in range(3)] + [0.05 * torch.randn(B, H, E, 4, device=d)]
+           for _ in range(2)]
+    xs = [torch.randn(1, B, D + 1, device=d) for _ in range(6)]
+    step = GraphedSRStep(layers, st0, xs[0], pre=pre)
+    st = [[t.clone() for t in s] for s in st0]
+    mask = torch.zeros(B, dtype=torch.bool, device=d)
+    mask[::3] = True
+    with torch.no_grad():
+        for i, x in enumerate(xs):
+            if i == 3:                      # episode ends for a third of the samples
+                step.reset(mask)
+                st = [[t * (~mask).float().view(B, 1, 1, 1) for t in s] for s in st]
+            got = step(x).clone()
+            h = pre(x)
+            for li, (sr, ff) in enumerate(layers):
+                h, new = sr(h, st[li])
+                st[li] = list(new)
+                h = ff(h)
+            assert orc.rel_max(got, h) < FWD_TOL, i
+    for a, b in zip(step.state, st):
+        for u, v in zip(a, b):
+            assert float((u - v).abs().max()) < FWD_TOL * E ** -0.5
