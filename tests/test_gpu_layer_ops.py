@@ -497,3 +497,51 @@ def test_graphed_actor_step_matches_eager():
     for a, b in zip(step.state, st):
         for u, v in zip(a, b):
             assert float((u - v).abs().max()) < FWD_TOL * E ** -0.5
+
+
+def test_layer_unroll_detached_bf16():
+    from srwm_b200.layer_ops import srwm_layer
+    N, H, T, E = 3, 2, 40, 64
+    x, base, shift, go, _ = _layer_inputs(N, H, T, E, 777, True)
+    x, go = x.bfloat16(), go.bfloat16()
+    done = torch.rand(N, T, generator=torch.Generator().manual_seed(8)) < 0.1
+    xo = x.double().requires_grad_()
+    bo = _leaf(base)
+    out_o, sh_o = lorc.srwm_unroll_detached(xo, bo, [s.double() for s in shift], done, True)
+    (out_o * go.double()).sum().backward()
+    d = _dev()
+    xd = x.to(d).requires_grad_()
+    bd = _leaf(base, torch.float32, d)
+    out, sh = srwm_layer(xd, *bd, shift=[s.to(d) for s in shift], done=done.to(d), detach_state=True)
+    (out * go.to(d)).sum().backward()
+    assert orc.rel_max(out.detach().float().cpu(), out_o.detach()) < BF16_TOL
+    assert orc.rel_max(xd.grad.float().cpu(), xo.grad) < BF16_TOL
+    assert orc.rel_max(bd[0].grad.cpu(), bo[0].grad) < GRAD_TOL
+    for a, b in zip(sh, sh_o):
+        assert float((a.cpu() - b).abs().max()) < FWD_TOL * E ** -0.5
+
+
+@pytest.mark.parametrize("dtype,lead", [(torch.float32, 1), (torch.float32, 3), (torch.bfloat16, 5), (torch.bfloat16, 7)])
+def test_delta_packed_rows_at_every_misalignment(dtype, lead):
+    """The packed rows may start anywhere on the element grid: shift the whole tensor by a few
+    elements inside its allocation so that every (address mod 16) case of the block staging occurs."""
+    from srwm_b200.layer_ops import delta_layer
+    L, B, H, E = 18, 2, 3, 16
+    RS = 3 * E + 1
+    g = torch.Generator().manual_seed(500 + lead)
+    raw = torch.randn(L, B, H * RS, generator=g).to(dtype)
+    go = torch.randn(B, H, L, E, generator=g).to(dtype)
+    ro = raw.double().requires_grad_()
+    out_o, _ = lorc.delta_layer(ro.view(L, B, H, RS).permute(1, 2, 0, 3), torch.zeros(B, H, E, E).double(), 0.0)
+    (out_o * go.double()).sum().backward()
+    d = _dev()
+    buf = torch.zeros(raw.numel() + 16, dtype=dtype, device=d)
+    rd = buf[lead:lead + raw.numel()].view(L, B, H * RS)
+    rd.copy_(raw)
+    rd.requires_grad_()
+    W = torch.empty(B, H, E, E, device=d)
+    out = delta_layer(rd.view(L, B, H, RS).permute(1, 2, 0, 3), W, zero_init=True)
+    (out * go.to(d)).sum().backward()
+    tol_f, tol_g = (FWD_TOL, GRAD_TOL) if dtype == torch.float32 else (BF16_TOL, BF16_TOL)
+    assert orc.rel_max(out.detach().float().cpu(), out_o.detach()) < tol_f
+    assert orc.rel_max(rd.grad.float().cpu(), ro.grad) < tol_g
