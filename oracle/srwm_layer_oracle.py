@@ -16,9 +16,12 @@ the SRWM operator, so that the fused layer-level entry points can be checked aga
                      the slow net's rows, sigmoid, ``elu + 1`` and the sum normalisation (with
                      the agents' 1e-5 in the denominator, layer.py:30-33), then the delta rule.
 
-The recurrence itself is ``srwm_oracle.srwm_loop`` / ``delta_loop`` (pinned against the reference's own
-self test).  Parity of these wrappers is pinned by construction only: they are the
-reference layers' lines around the operator, restated; the reference has no test for them.
+The recurrence itself is ``srwm_oracle.srwm_loop`` / ``delta_loop`` (pinned against the reference's
+own self test).  Parity pin of these wrappers: ``oracle/pin_reference_layers.py`` runs the
+reference's own layer classes (``SRWMlayer``, both ``FastFFlayer`` s, ``SRlayer`` under the learner's
+loop) on the CPU in float64 and stores every tensor of those runs under ``tests/golden/layer_*.pt``;
+``tests/test_layer_golden.py`` checks the functions below against them (outputs to 1e-10, all
+gradients to 1e-9).
 
 Only ``tests/`` may import this module.
 """
