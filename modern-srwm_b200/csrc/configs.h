@@ -31,9 +31,9 @@
   Y(64, 8, 16, true, 3, true, 2)    \
   Y(16, 2, 16, true, 8, true, 2)    \
   Y(16, 3, 16, true, 16, true, 2)   \
-  Y(32, 0, 16, true, 8, true, 1)    \
+  Y(32, 0, 16, true, 8, true, 2)    \
   Y(32, 4, 16, true, 8, false, 1)   \
-  Y(32, 5, 16, true, 8, true, 2)    \
+  Y(32, 5, 16, true, 8, true, 1)    \
   Y(32, 6, 16, true, 8, true, 4)    \
   Y(32, 7, 16, true, 12, true, 4)
 
