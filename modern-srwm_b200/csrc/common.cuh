@@ -243,6 +243,15 @@ __device__ __forceinline__ float allreduce_rows_max(float v) {
   for (int off = 1; off < NRG; off <<= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, off));
   return v;
 }
+// over the NP row parts of the column layouts: part p of a warp is its lanes [p*32/NP, (p+1)*32/NP)
+// (a broadcast operand load then sees one address per half / quarter warp, which the shared-memory
+// pipe serves in as many wavefronts as there are parts; interleaved parts cost twice that)
+template <int NP>
+__device__ __forceinline__ float allreduce_parts(float v) {
+#pragma unroll
+  for (int off = 32 / NP; off < 32; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
 template <int NRG>
 __device__ __forceinline__ float allreduce_cols(float v) {   // over the column groups of this warp
 #pragma unroll

@@ -60,12 +60,20 @@
   X(16, 0, 32, 4, 16, true, 8)   \
   X(32, 0, 32, 8, 16, true, 12)  \
   X(32, 1, 64, 8, 16, true, 8)   \
-  X(64, 0, 64, 16, 8, true, 8)   \
+  X(64, 6, 64, 16, 8, true, 8)   \
   X(64, 1, 64, 32, 8, true, 8)   \
   X(64, 2, 64, 64, 8, true, 8)   \
   X(64, 3, 128, 16, 8, true, 6)  \
   X(64, 4, 32, 16, 8, true, 10)  \
   X(64, 5, 64, 16, 8, false, 8)
+
+// Column-layout delta forward: Y(E, variant, P, T, PK, MINB, NRP); the default at E = 64
+#define DELTA_FWD_COL_CONFIGS(Y)  \
+  Y(64, 0, 32, 8, true, 8, 1)     \
+  Y(64, 7, 32, 8, true, 8, 2)     \
+  Y(64, 8, 64, 8, true, 7, 2)     \
+  Y(32, 2, 32, 16, true, 16, 1)   \
+  Y(32, 3, 32, 16, true, 16, 2)
 
 #define DELTA_BWD_CONFIGS(X)     \
   X(8, 0, 32, 2, 16, true, 8)    \

@@ -289,6 +289,183 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
 }
 
 // ---------------------------------------------------------------------------------------
+// Forward, column layout (E = 32 or 64): P = 32 or 64 threads per sequence, thread (cq, rp) holds
+// CPL adjacent columns x E/NRP rows of W as row pairs; the warps of a sequence own disjoint
+// columns and never talk to each other.  Both products reduce over rows, so with whole
+// columns per lane (NRP = 1) nothing in a step crosses lanes at all: k and q are read from the
+// staged rows as 16-byte shared-memory broadcasts, v / out / v_old / v_insert are per column.
+//   pass A:  v_old[c] = sum_r k[r] W[r][c]          ins[c] = beta (v[c] - v_old[c])
+//   pass B:  W[r][c] += k[r] ins[c]  and, with the updated value, out[c] += q[r] W[r][c]
+// NRP = 2 splits the rows of a column group over two lanes (half the broadcast loads, one
+// shuffle stage per column sum).  16-bit streams are converted to fp32 rows once per chunk.
+// No barrier exists in this kernel beyond the hand-over of a staged chunk.
+// ---------------------------------------------------------------------------------------
+template <typename TIO, int E, int T>
+struct DeltaFwdColSmem {
+  static constexpr int ROW_IO = E * (int)sizeof(TIO);
+  static constexpr int ROW_F = E * 4;
+  static constexpr int BETA_BYTES = ((T * 4 + 15) / 16) * 16;
+  static constexpr int IN_BYTES = 3 * T * ROW_IO + BETA_BYTES;
+  static constexpr int CONV_BYTES = sizeof(TIO) == 4 ? 0 : 2 * T * ROW_F;   // k, q as fp32 rows
+  static constexpr int OUT_BYTES = T * ROW_IO + 2 * T * ROW_F;
+  static constexpr int TOTAL = 2 * IN_BYTES + CONV_BYTES + OUT_BYTES;
+};
+
+template <typename TIO, int E, int P, int T, bool PK, int MINB, int NRP>
+__global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdParams p) {
+  using SM = DeltaFwdColSmem<TIO, E, T>;
+  constexpr int CPL = (E * NRP) / P, RL = E / NRP, RL2 = RL / 2;
+  static_assert(NRP == 1 || NRP == 2, "row parts per column group");
+  static_assert(P % 32 == 0 && CPL >= 1 && CPL * P == E * NRP && RL % 4 == 0, "bad column-layout shape");
+  const int lane = threadIdx.x;   // thread index within the sequence's P threads
+  constexpr int LPP = 32 / NRP;   // lanes per row part within a warp
+  const int rp = (lane % 32) / LPP, c0 = ((lane / 32) * LPP + lane % LPP) * CPL;
+  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
+  const bool save = !(p.flags & 1u);
+
+  extern __shared__ __align__(16) unsigned char smem[];
+  float* conv = reinterpret_cast<float*>(smem + 2 * SM::IN_BYTES);   // [2][T][E] k, q (16-bit streams)
+  unsigned char* s_out = smem + 2 * SM::IN_BYTES + SM::CONV_BYTES;
+  TIO* so = reinterpret_cast<TIO*>(s_out);
+  float* svold = reinterpret_cast<float*>(s_out + T * SM::ROW_IO);
+  float* svins = svold + T * E;
+
+  // local row r of row part rp is global row ((r/4)*NRP + rp)*4 + r%4 (row quads interleaved over
+  // the row parts: the lanes of a column group read an operand vector as adjacent 16-byte pieces)
+  auto grow = [&](int r) { return ((r / 4) * NRP + rp) * 4 + (r % 4); };
+  u64 W[RL2][CPL];
+  float* Wg = p.W.mat(n, h);
+#pragma unroll
+  for (int e2 = 0; e2 < RL2; ++e2) {
+    float a[CPL], b[CPL];
+    ld_vec<CPL>(Wg + grow(2 * e2) * E + c0, a);
+    ld_vec<CPL>(Wg + grow(2 * e2 + 1) * E + c0, b);
+#pragma unroll
+    for (int c = 0; c < CPL; ++c) W[e2][c] = pack2(a[c], b[c]);
+  }
+
+  const int L = p.L;
+  const int nchunks = (L + T - 1) / T;
+  auto in_buf = [&](int b) { return smem + b * SM::IN_BYTES; };
+  auto stage_chunk = [&](int c) {
+    const int t0 = c * T, nt = min(T, L - t0);
+    unsigned char* ib = in_buf(c & 1);
+    stage_rows<SM::ROW_IO, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, lane);
+    stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.K.row(n, h, t0), p.K.sl, nt, lane);
+    stage_rows<SM::ROW_IO, P>(ib + 2 * T * SM::ROW_IO, p.V.row(n, h, t0), p.V.sl, nt, lane);
+  };
+  auto beta_buf = [&](int b) { return reinterpret_cast<float*>(in_buf(b) + 3 * T * SM::ROW_IO); };
+  static_assert(T <= 32, "one thread per step loads beta");
+
+  stage_chunk(0);
+  cp_async_commit();
+  if (lane < min(T, L)) beta_buf(0)[lane] = to_f32(*reinterpret_cast<const TIO*>(p.beta.row(n, h, lane)));
+
+  for (int c = 0; c < nchunks; ++c) {
+    const int t0 = c * T, nt = min(T, L - t0);
+    const bool has_next = (c + 1 < nchunks);
+    const int nt_next = has_next ? min(T, L - (t0 + T)) : 0;
+    float bnext = 0.f;
+    if (has_next) {
+      stage_chunk(c + 1);
+      if (lane < nt_next) bnext = to_f32(*reinterpret_cast<const TIO*>(p.beta.row(n, h, t0 + T + lane)));
+    }
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();   // chunk c staged; the output stage of the previous chunk has been flushed
+
+    const unsigned char* ib = in_buf(c & 1);
+    const float *sq, *sk;
+    if constexpr (sizeof(TIO) == 4) {
+      sq = reinterpret_cast<const float*>(ib);
+      sk = reinterpret_cast<const float*>(ib + T * SM::ROW_IO);
+    } else {
+      convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib), conv, nt, lane);
+      convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO), conv + T * E, nt, lane);
+      __syncthreads();
+      sq = conv;
+      sk = conv + T * E;
+    }
+    const TIO* sv = reinterpret_cast<const TIO*>(ib + 2 * T * SM::ROW_IO);
+    const float* sb = beta_buf(c & 1);
+
+#pragma unroll 1
+    for (int t = 0; t < nt; ++t) {
+      const float4* k4 = reinterpret_cast<const float4*>(sk + t * E);
+      const float4* q4 = reinterpret_cast<const float4*>(sq + t * E);
+      // ---- pass A: v_old = k.W on this lane's columns ------------------------------------
+      u64 a0[CPL], a1[CPL];
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) { a0[cc] = 0ull; a1[cc] = 0ull; }
+#pragma unroll
+      for (int e4 = 0; e4 < RL / 4; ++e4) {
+        const float4 kv = k4[e4 * NRP + rp];
+        const u64 k0 = pack2(kv.x, kv.y), k1 = pack2(kv.z, kv.w);
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) {
+          a0[cc] = fma2<PK>(k0, W[2 * e4][cc], a0[cc]);
+          a1[cc] = fma2<PK>(k1, W[2 * e4 + 1][cc], a1[cc]);
+        }
+      }
+      float vc[CPL], vold[CPL], ins[CPL];
+      ld_vec<CPL>(sv + t * E + c0, vc);
+      const float bt = sb[t];
+      u64 ins2[CPL];
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) {
+        vold[cc] = allreduce_parts<NRP>(hsum2(a0[cc]) + hsum2(a1[cc]));
+        ins[cc] = bt * (vc[cc] - vold[cc]);
+        ins2[cc] = dup2(ins[cc]);
+        a0[cc] = 0ull;
+        a1[cc] = 0ull;
+      }
+      // ---- pass B: W += k^T ins, out = q.W (updated) --------------------------------------
+#pragma unroll
+      for (int e4 = 0; e4 < RL / 4; ++e4) {
+        const float4 kv = k4[e4 * NRP + rp];
+        const float4 qv = q4[e4 * NRP + rp];
+        const u64 k0 = pack2(kv.x, kv.y), k1 = pack2(kv.z, kv.w);
+        const u64 q0 = pack2(qv.x, qv.y), q1 = pack2(qv.z, qv.w);
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) {
+          W[2 * e4][cc] = fma2<PK>(k0, ins2[cc], W[2 * e4][cc]);
+          W[2 * e4 + 1][cc] = fma2<PK>(k1, ins2[cc], W[2 * e4 + 1][cc]);
+          a0[cc] = fma2<PK>(q0, W[2 * e4][cc], a0[cc]);
+          a1[cc] = fma2<PK>(q1, W[2 * e4 + 1][cc], a1[cc]);
+        }
+      }
+      float o[CPL];
+#pragma unroll
+      for (int cc = 0; cc < CPL; ++cc) o[cc] = allreduce_parts<NRP>(hsum2(a0[cc]) + hsum2(a1[cc]));
+      if (rp == 0) {
+        st_vec<CPL>(so + t * E + c0, o);
+        if (save) {
+          st_vec<CPL>(svold + t * E + c0, vold);
+          st_vec<CPL>(svins + t * E + c0, ins);
+        }
+      }
+    }
+
+    if (has_next && lane < nt_next) beta_buf((c + 1) & 1)[lane] = bnext;
+    __syncthreads();
+    flush_rows<SM::ROW_IO, P>(p.out.row(n, h, t0), p.out.sl, so, nt, lane);
+    if (save) {
+      flush_rows<SM::ROW_F, P>(p.v_old.row(n, h, t0), p.v_old.sl, svold, nt, lane);
+      flush_rows<SM::ROW_F, P>(p.v_ins.row(n, h, t0), p.v_ins.sl, svins, nt, lane);
+    }
+  }
+
+#pragma unroll
+  for (int e2 = 0; e2 < RL2; ++e2) {
+    float a[CPL], b[CPL];
+#pragma unroll
+    for (int cc = 0; cc < CPL; ++cc) unpack2(W[e2][cc], a[cc], b[cc]);
+    st_vec<CPL>(Wg + grow(2 * e2) * E + c0, a);
+    st_vec<CPL>(Wg + grow(2 * e2 + 1) * E + c0, b);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
 // Backward.  With G = dL/dW_t carried backwards in time and g = dL/dout_t:
 //   G += q^T g ; gq = W_t g ; r = k.G ; gv = beta r ; gbeta = r.(v - v_old)
 //   gk = G ins + W_{t-1} (-beta r) ; W_{t-1} = W_t - k^T ins ; G += k^T (-beta r)

@@ -17,7 +17,7 @@ typedef float TIO;
 template <int E, int V, int P, int R, int T, bool PK, int MINB>
 int run(const DeltaFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
   if (p.flags & F_PACKED) {
-    if constexpr (V == 0) {
+    if constexpr (V == (E == 64 ? 6 : 0)) {
       constexpr int smem = DeltaFwdSmem<TIO, E, T, true>::TOTAL;
       if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; }
       if (describe_only) return 0;
@@ -34,6 +34,16 @@ int run(const DeltaFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int
   return launch_kernel(delta_fwd_kernel<TIO, E, P, R, T, PK, MINB>, p, grid, P, smem, s, &dev_mask, cuda_err);
 }
 
+template <int E, int P, int T, bool PK, int MINB, int NRP>
+int run_col(const DeltaFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
+  if (p.flags & F_PACKED) return -6;
+  constexpr int smem = DeltaFwdColSmem<TIO, E, T>::TOTAL;
+  if (info) { info->P = P; info->R = E / NRP; info->T = T; info->smem = smem; }
+  if (describe_only) return 0;
+  static unsigned long long dev_mask = 0;
+  return launch_kernel(delta_fwd_col_kernel<TIO, E, P, T, PK, MINB, NRP>, p, grid, P, smem, s, &dev_mask, cuda_err);
+}
+
 }  // namespace
 
 #if SRWM_TIO_BF16
@@ -43,10 +53,20 @@ int dispatch_delta_fwd_f32(
 #endif
     int E, int variant, const DeltaFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only,
     int* cuda_err) {
+  // the packed (layer-level) form exists for the tile kernel only: its default at E = 64 is variant 6
+  if ((p.flags & F_PACKED) && E == 64 && variant == 0) variant = 6;
+  // default at E = 64: one warp per sequence when the grid can fill the SMs; with fewer sequences the
+  // per-step latency of a single warp shows, and two warps per sequence (variant 8) are faster
+  // (measured: 256 sequences 201 vs 261 us, 1184 sequences 900 vs 814 us)
+  if (!(p.flags & F_PACKED) && E == 64 && variant == 0 && !describe_only && grid < 592) variant = 8;
 #define X(E_, V_, P_, R_, T_, PK_, MINB_) \
   if (E == E_ && variant == V_) return run<E_, V_, P_, R_, T_, PK_, MINB_>(p, grid, s, info, describe_only, cuda_err);
   DELTA_FWD_CONFIGS(X)
 #undef X
+#define Y(E_, V_, P_, T_, PK_, MINB_, NRP_) \
+  if (E == E_ && variant == V_) return run_col<E_, P_, T_, PK_, MINB_, NRP_>(p, grid, s, info, describe_only, cuda_err);
+  DELTA_FWD_COL_CONFIGS(Y)
+#undef Y
   return (E == 8 || E == 16 || E == 32 || E == 64) ? -6 : -3;
 }
 

@@ -435,7 +435,8 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
   static_assert(CPL >= 1 && (CPL * 32) == E * NRP && RL % 4 == 0 && (DUP || CPL % NRP == 0), "bad column-layout shape");
   const int tid = threadIdx.x;
   const int warp = tid / 32, lane = tid % 32;
-  const int rp = lane % NRP, c0 = (lane / NRP) * CPL;
+  constexpr int LPP = 32 / NRP;   // lanes per row part: part rp is lanes [rp*LPP, (rp+1)*LPP) of the warp
+  const int rp = lane / LPP, c0 = (lane % LPP) * CPL;
   const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
   const bool save = !(p.flags & 1u);
   const int jb = lane / 8, r8 = lane % 8;   // warp 0: w_b column / row eighth of this lane
@@ -580,10 +581,10 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       int cs;
       if constexpr (DUP) {
 #pragma unroll
-        for (int i = 0; i < CPL; ++i) vs[i] = allreduce_rows<NRP>(v[i]);   // every row-part lane gets the column
+        for (int i = 0; i < CPL; ++i) vs[i] = allreduce_parts<NRP>(v[i]);   // every row-part lane gets the column
         cs = c0;
       } else {
-        reduce_scatter<CPL, NRP, 1>(v, lane);   // lane rp keeps columns c0 + rp*VPL .. + VPL
+        reduce_scatter<CPL, NRP, LPP>(v, lane);   // lane rp keeps columns c0 + rp*VPL .. + VPL
 #pragma unroll
         for (int i = 0; i < VPL; ++i) vs[i] = v[i];
         cs = c0 + rp * VPL;
@@ -653,7 +654,7 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
       u64 ins2[CPL];
 #pragma unroll
       for (int cc = 0; cc < CPL; ++cc) {
-        v[cc] = allreduce_rows<NRP>(hsum2(a0[cc]) + hsum2(a1[cc]));
+        v[cc] = allreduce_parts<NRP>(hsum2(a0[cc]) + hsum2(a1[cc]));
         ins2[cc] = dup2(bz * v[cc]);
       }
       if (rp == 0) st_vec<CPL>(sdz + t * E + c0, v);
