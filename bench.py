@@ -835,7 +835,7 @@ def run_layer_prof(args):
         rows = raw.view(L_, B, H, RS).permute(1, 2, 0, 3)
         go = OpBench._big_randn((B, H, L_, E), g, torch.bfloat16)
         W = torch.empty(B, H, E, E, device=device)
-        names = ("delta_fwd_kernel<PACKED>", "delta_bwd_kernel<PACKED>")
+        names = ("delta_fwd_col_kernel<PACKED>", "delta_bwd_kernel<PACKED>")
         fbytes = B * H * (L_ * (RS * 2 + E * 2 + 2 * E * 4) + E * E * 4)
         bbytes = B * H * (L_ * (2 * RS * 2 + E * 2 + 2 * E * 4) + 2 * E * E * 4)
 

@@ -300,20 +300,24 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
 // shuffle stage per column sum).  16-bit streams are converted to fp32 rows once per chunk.
 // No barrier exists in this kernel beyond the hand-over of a staged chunk.
 // ---------------------------------------------------------------------------------------
-template <typename TIO, int E, int T>
+template <typename TIO, int E, int T, bool PACKED = false>
 struct DeltaFwdColSmem {
   static constexpr int ROW_IO = E * (int)sizeof(TIO);
   static constexpr int ROW_F = E * 4;
   static constexpr int BETA_BYTES = ((T * 4 + 15) / 16) * 16;
-  static constexpr int IN_BYTES = 3 * T * ROW_IO + BETA_BYTES;
-  static constexpr int CONV_BYTES = sizeof(TIO) == 4 ? 0 : 2 * T * ROW_F;   // k, q as fp32 rows
+  static constexpr int RSB = (3 * E + 1) * (int)sizeof(TIO);
+  static constexpr int PK_PITCH = ((RSB + 30) / 16) * 16;
+  static constexpr int IN_BYTES = PACKED ? T * PK_PITCH : 3 * T * ROW_IO + BETA_BYTES;
+  // k, q as fp32 rows (16-bit streams), or the prepared q, k, v, beta of the packed form
+  static constexpr int CONV_BYTES = PACKED ? 3 * T * ROW_F + BETA_BYTES : (sizeof(TIO) == 4 ? 0 : 2 * T * ROW_F);
   static constexpr int OUT_BYTES = T * ROW_IO + 2 * T * ROW_F;
   static constexpr int TOTAL = 2 * IN_BYTES + CONV_BYTES + OUT_BYTES;
 };
 
-template <typename TIO, int E, int P, int T, bool PK, int MINB, int NRP>
+template <typename TIO, int E, int P, int T, bool PK, int MINB, int NRP, bool PACKED = false>
 __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdParams p) {
-  using SM = DeltaFwdColSmem<TIO, E, T>;
+  using SM = DeltaFwdColSmem<TIO, E, T, PACKED>;
+  using TS = typename std::conditional<PACKED, float, TIO>::type;   // element type of the staged v rows
   constexpr int CPL = (E * NRP) / P, RL = E / NRP, RL2 = RL / 2;
   static_assert(NRP == 1 || NRP == 2, "row parts per column group");
   static_assert(P % 32 == 0 && CPL >= 1 && CPL * P == E * NRP && RL % 4 == 0, "bad column-layout shape");
@@ -335,11 +339,17 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdPa
   auto grow = [&](int r) { return ((r / 4) * NRP + rp) * 4 + (r % 4); };
   u64 W[RL2][CPL];
   float* Wg = p.W.mat(n, h);
+  const bool zero_init = PACKED && (p.flags & F_ZERO_INIT);
 #pragma unroll
   for (int e2 = 0; e2 < RL2; ++e2) {
     float a[CPL], b[CPL];
-    ld_vec<CPL>(Wg + grow(2 * e2) * E + c0, a);
-    ld_vec<CPL>(Wg + grow(2 * e2 + 1) * E + c0, b);
+    if (zero_init) {
+#pragma unroll
+      for (int c = 0; c < CPL; ++c) { a[c] = 0.f; b[c] = 0.f; }
+    } else {
+      ld_vec<CPL>(Wg + grow(2 * e2) * E + c0, a);
+      ld_vec<CPL>(Wg + grow(2 * e2 + 1) * E + c0, b);
+    }
 #pragma unroll
     for (int c = 0; c < CPL; ++c) W[e2][c] = pack2(a[c], b[c]);
   }
@@ -350,16 +360,21 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdPa
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
     unsigned char* ib = in_buf(c & 1);
-    stage_rows<SM::ROW_IO, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, lane);
-    stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.K.row(n, h, t0), p.K.sl, nt, lane);
-    stage_rows<SM::ROW_IO, P>(ib + 2 * T * SM::ROW_IO, p.V.row(n, h, t0), p.V.sl, nt, lane);
+    if constexpr (PACKED) {
+      stage_packed_rows<SM::RSB, SM::PK_PITCH, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, lane);
+    } else {
+      stage_rows<SM::ROW_IO, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, lane);
+      stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.K.row(n, h, t0), p.K.sl, nt, lane);
+      stage_rows<SM::ROW_IO, P>(ib + 2 * T * SM::ROW_IO, p.V.row(n, h, t0), p.V.sl, nt, lane);
+    }
   };
   auto beta_buf = [&](int b) { return reinterpret_cast<float*>(in_buf(b) + 3 * T * SM::ROW_IO); };
   static_assert(T <= 32, "one thread per step loads beta");
 
   stage_chunk(0);
   cp_async_commit();
-  if (lane < min(T, L)) beta_buf(0)[lane] = to_f32(*reinterpret_cast<const TIO*>(p.beta.row(n, h, lane)));
+  if constexpr (!PACKED)
+    if (lane < min(T, L)) beta_buf(0)[lane] = to_f32(*reinterpret_cast<const TIO*>(p.beta.row(n, h, lane)));
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * T, nt = min(T, L - t0);
@@ -368,26 +383,38 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdPa
     float bnext = 0.f;
     if (has_next) {
       stage_chunk(c + 1);
-      if (lane < nt_next) bnext = to_f32(*reinterpret_cast<const TIO*>(p.beta.row(n, h, t0 + T + lane)));
+      if constexpr (!PACKED)
+        if (lane < nt_next) bnext = to_f32(*reinterpret_cast<const TIO*>(p.beta.row(n, h, t0 + T + lane)));
     }
     cp_async_commit();
     cp_async_wait<1>();
     __syncthreads();   // chunk c staged; the output stage of the previous chunk has been flushed
 
     const unsigned char* ib = in_buf(c & 1);
-    const float *sq, *sk;
-    if constexpr (sizeof(TIO) == 4) {
-      sq = reinterpret_cast<const float*>(ib);
-      sk = reinterpret_cast<const float*>(ib + T * SM::ROW_IO);
-    } else {
-      convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib), conv, nt, lane);
-      convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO), conv + T * E, nt, lane);
+    const float *sq, *sk, *sb;
+    const TS* sv;
+    if constexpr (PACKED) {
+      prepare_packed_rows<TIO, E, P, T, SM::PK_PITCH>(ib, p.Q.row(n, h, t0), p.Q.sl, p.eps, conv, conv + T * E,
+                                                      conv + 2 * T * E, conv + 3 * T * E, nullptr, nullptr, nt, lane);
       __syncthreads();
       sq = conv;
       sk = conv + T * E;
+      sv = conv + 2 * T * E;
+      sb = conv + 3 * T * E;
+    } else {
+      if constexpr (sizeof(TIO) == 4) {
+        sq = reinterpret_cast<const float*>(ib);
+        sk = reinterpret_cast<const float*>(ib + T * SM::ROW_IO);
+      } else {
+        convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib), conv, nt, lane);
+        convert_rows<TIO, E, P>(reinterpret_cast<const TIO*>(ib + T * SM::ROW_IO), conv + T * E, nt, lane);
+        __syncthreads();
+        sq = conv;
+        sk = conv + T * E;
+      }
+      sv = reinterpret_cast<const TS*>(ib + 2 * T * SM::ROW_IO);
+      sb = beta_buf(c & 1);
     }
-    const TIO* sv = reinterpret_cast<const TIO*>(ib + 2 * T * SM::ROW_IO);
-    const float* sb = beta_buf(c & 1);
 
 #pragma unroll 1
     for (int t = 0; t < nt; ++t) {
@@ -446,7 +473,8 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdPa
       }
     }
 
-    if (has_next && lane < nt_next) beta_buf((c + 1) & 1)[lane] = bnext;
+    if constexpr (!PACKED)
+      if (has_next && lane < nt_next) beta_buf((c + 1) & 1)[lane] = bnext;
     __syncthreads();
     flush_rows<SM::ROW_IO, P>(p.out.row(n, h, t0), p.out.sl, so, nt, lane);
     if (save) {

@@ -36,7 +36,18 @@ int run(const DeltaFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int
 
 template <int E, int P, int T, bool PK, int MINB, int NRP>
 int run_col(const DeltaFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
-  if (p.flags & F_PACKED) return -6;
+  if (p.flags & F_PACKED) {
+    if constexpr (E == 64 && NRP == 1 && P == 32) {   // the packed form of the default configuration
+      constexpr int smem = DeltaFwdColSmem<TIO, E, T, true>::TOTAL;
+      if (info) { info->P = P; info->R = E / NRP; info->T = T; info->smem = smem; }
+      if (describe_only) return 0;
+      static unsigned long long dev_mask_pk = 0;
+      return launch_kernel(delta_fwd_col_kernel<TIO, E, P, T, PK, MINB, NRP, true>, p, grid, P, smem, s, &dev_mask_pk,
+                           cuda_err);
+    } else {
+      return -6;
+    }
+  }
   constexpr int smem = DeltaFwdColSmem<TIO, E, T>::TOTAL;
   if (info) { info->P = P; info->R = E / NRP; info->T = T; info->smem = smem; }
   if (describe_only) return 0;
@@ -53,8 +64,9 @@ int dispatch_delta_fwd_f32(
 #endif
     int E, int variant, const DeltaFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only,
     int* cuda_err) {
-  // the packed (layer-level) form exists for the tile kernel only: its default at E = 64 is variant 6
-  if ((p.flags & F_PACKED) && E == 64 && variant == 0) variant = 6;
+  // the packed (layer-level) form at E = 64: column kernel (variant 0) when the grid fills the SMs,
+  // register tiles (variant 6) otherwise
+  if ((p.flags & F_PACKED) && E == 64 && variant == 0 && !describe_only && grid < 592) variant = 6;
   // default at E = 64: one warp per sequence when the grid can fill the SMs; with fewer sequences the
   // per-step latency of a single warp shows, and two warps per sequence (variant 8) are faster
   // (measured: 256 sequences 201 vs 261 us, 1184 sequences 900 vs 814 us)

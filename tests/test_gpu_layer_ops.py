@@ -545,3 +545,27 @@ def test_delta_packed_rows_at_every_misalignment(dtype, lead):
     tol_f, tol_g = (FWD_TOL, GRAD_TOL) if dtype == torch.float32 else (BF16_TOL, BF16_TOL)
     assert orc.rel_max(out.detach().float().cpu(), out_o.detach()) < tol_f
     assert orc.rel_max(rd.grad.float().cpu(), ro.grad) < tol_g
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_delta_packed_layer_large_grid_column_kernel(dtype):
+    """With enough sequences to fill the GPU the packed d=64 forward runs in the column layout
+    (one warp per sequence); same checks as for the small cases."""
+    from srwm_b200.layer_ops import delta_layer
+    L, B, H, E = 19, 40, 16, 64      # 640 sequences
+    RS = 3 * E + 1
+    g = torch.Generator().manual_seed(91)
+    raw = torch.randn(L, B, H * RS, generator=g).to(dtype)
+    go = torch.randn(B, H, L, E, generator=g).to(dtype)
+    ro = raw.double().requires_grad_()
+    out_o, WL = lorc.delta_layer(ro.view(L, B, H, RS).permute(1, 2, 0, 3), torch.zeros(B, H, E, E).double(), 1e-5)
+    (out_o * go.double()).sum().backward()
+    d = _dev()
+    rd = raw.to(d).requires_grad_()
+    W = torch.full((B, H, E, E), float("nan"), device=d)
+    out = delta_layer(rd.view(L, B, H, RS).permute(1, 2, 0, 3), W, norm_eps=1e-5, zero_init=True)
+    tol_f, tol_g = (FWD_TOL, GRAD_TOL) if dtype == torch.float32 else (BF16_TOL, BF16_TOL)
+    assert orc.rel_max(out.detach().float().cpu(), out_o.detach()) < tol_f
+    assert orc.rel_max(W.cpu(), WL.detach()) < FWD_TOL
+    (out * go.to(d)).sum().backward()
+    assert orc.rel_max(rd.grad.float().cpu(), ro.grad) < tol_g
