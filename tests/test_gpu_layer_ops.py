@@ -569,3 +569,34 @@ def test_delta_packed_layer_large_grid_column_kernel(dtype):
     assert orc.rel_max(W.cpu(), WL.detach()) < FWD_TOL
     (out * go.to(d)).sum().backward()
     assert orc.rel_max(rd.grad.float().cpu(), ro.grad) < tol_g
+
+
+def test_layer_call_at_scale_matches_plain_operator_composition():
+    """Several waves of sequences, many chunks, bf16: the fused layer call against torch softmax +
+    repeat + the plain operator (two different kernel instantiations of this library)."""
+    import srwm_b200 as sb
+    from srwm_b200.layer_ops import srwm_layer
+    d = _dev()
+    N, H, L, E = 80, 16, 300, 64
+    g = torch.Generator(device=d).manual_seed(17)
+    x = torch.randn(N, H, L, E, device=d, generator=g).bfloat16()
+    go = torch.randn(N, H, L, E, device=d, generator=g).bfloat16()
+    std = E ** -0.5
+    base = [torch.randn(1, H, E, E, device=d, generator=g) * std for _ in range(3)]
+    base.append(torch.randn(1, H, E, 4, device=d, generator=g) * std)
+    shift = [0.05 * std * torch.randn(N, H, E, w.shape[-1], device=d, generator=g) for w in base]
+    x1 = x.clone().requires_grad_()
+    b1 = [b.clone().requires_grad_() for b in base]
+    out1, sh1 = srwm_layer(x1, *b1, shift=shift)
+    (out1.float() * go.float()).sum().backward()
+    x2 = x.clone().float().requires_grad_()
+    b2 = [b.clone().requires_grad_() for b in base]
+    W = [s + b.repeat(N, 1, 1, 1) for s, b in zip(shift, b2)]
+    out2 = sb.self_ref_v0(torch.softmax(x2, -1), *W)      # fp32 activations: the tighter of the two
+    (out2 * go.float()).sum().backward()
+    assert orc.rel_max(out1.detach().float(), out2.detach()) < BF16_TOL
+    assert orc.rel_max(x1.grad.float(), x2.grad) < BF16_TOL
+    for a, b in zip(b1, b2):
+        assert orc.rel_max(a.grad, b.grad) < 2e-2      # bf16 activations feed a sum over 80 x 300 steps
+    for a, w, b in zip(sh1, W, b2):
+        assert float((a.detach() - (w.detach() - b.detach())).abs().max()) < 5e-3 * std
