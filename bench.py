@@ -865,6 +865,62 @@ def run_layer_prof(args):
                       "peak_source": f"of {peak_kind}"}), flush=True)
 
 
+def run_chunkwise_probe(args):
+    """Feasibility measurement for a chunkwise (UT-transform) delta-rule forward on tensor cores: the
+    chunk recursion written with torch batched matmuls (cuBLAS; chunk 64, fp32 triangular solve) at
+    three operand precisions, against this library's sequential kernel -- accuracy of the fp32
+    saved tensor v_insert and wall time.  A measurement aid, not a product path."""
+    import srwm_b200 as sb
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    N, H, L_, E, C = 64, 16, 2048, 64, 64
+    g = torch.Generator(device=device).manual_seed(1)
+    Q = torch.softmax(torch.randn(N, H, L_, E, device=device, generator=g), -1).bfloat16()
+    K = torch.softmax(torch.randn(N, H, L_, E, device=device, generator=g), -1).bfloat16()
+    V = torch.randn(N, H, L_, E, device=device, generator=g).bfloat16()
+    Bt = torch.sigmoid(torch.randn(N, H, L_, 1, device=device, generator=g)).bfloat16()
+    W = torch.zeros(N, H, E, E, device=device)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sb.delta_forward(Q, K, V, Bt, W)
+    W.zero_()
+    e0.record()
+    _, saved = sb.delta_forward(Q, K, V, Bt, W)
+    e1.record()
+    torch.cuda.synchronize(device)
+    seq_ms = e0.elapsed_time(e1)
+    ins_ref = saved[1]
+    eye = torch.eye(C, device=device)
+
+    def chunkwise(mm_dtype, tf32):
+        torch.backends.cuda.matmul.allow_tf32 = tf32
+        mm = (lambda a, b: a @ b) if mm_dtype is None else (lambda a, b: (a.to(mm_dtype) @ b.to(mm_dtype)).float())
+        Wc = torch.zeros(N, H, E, E, device=device)
+        ins = []
+        for c in range(L_ // C):
+            sl = slice(c * C, (c + 1) * C)
+            q, k, v, b = (t[:, :, sl].float() for t in (Q, K, V, Bt))
+            A = torch.tril(b * mm(k, k.transpose(-1, -2)), -1)
+            U = torch.linalg.solve_triangular(eye + A, b * (v - mm(k, Wc)), upper=False)
+            _ = mm(q, Wc) + mm(torch.tril(mm(q, k.transpose(-1, -2))), U)
+            Wc = Wc + mm(k.transpose(-1, -2), U)
+            ins.append(U)
+        return torch.cat(ins, 2)
+
+    res = {}
+    for name, dt, tf in (("fp32", None, False), ("tf32", None, True), ("bf16", torch.bfloat16, False)):
+        for _ in range(2):
+            torch.cuda.synchronize(device)
+            t0 = time.perf_counter()
+            u = chunkwise(dt, tf)
+            torch.cuda.synchronize(device)
+            t1 = time.perf_counter()
+        res[name] = {"v_insert_max_rel_err": float((u - ins_ref).abs().max() / ins_ref.abs().max()),
+                     "cublas_composition_ms": (t1 - t0) * 1e3}
+    torch.backends.cuda.matmul.allow_tf32 = False
+    print(json.dumps({"workload": f"delta forward, {N * H} sequences x {L_} steps, d=64, bf16 streams, chunk {C}",
+                      "sequential_kernel_ms": seq_ms, "chunkwise": res}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -881,8 +937,12 @@ def main():
                     help="layer-level timings: fused layer call vs torch ops around the operator")
     ap.add_argument("--layer-prof", choices=["srwm", "delta"], default=None,
                     help="layer-level kernels on a capture-sized workload (for profiler runs)")
+    ap.add_argument("--chunkwise-probe", action="store_true",
+                    help="accuracy / time of a chunkwise delta forward written with library matmuls")
     args = ap.parse_args()
-    if args.layer_prof:
+    if args.chunkwise_probe:
+        run_chunkwise_probe(args)
+    elif args.layer_prof:
         run_layer_prof(args)
     elif args.layer_table:
         run_layer_table(args)
