@@ -9,11 +9,14 @@
 //   d_Z = (q - k).W_Z ;  W_Z += k^T (b_Z d_Z)               for Z in {y, q, k, b}
 // and the update is applied at every step, the last one included.
 //
-// The three E x E blocks W_y, W_q, W_k share one register tiling (common.cuh); the small
-// E x 4 block w_b lives transposed in shared memory and is handled by one column group
-// per column (column j by group j*NCG/4).  One block-wide barrier per time step, placed
-// where the softmax needs all of q~ / k~ (forward) or where the row sums of the backward
-// have to cross warps.
+// Kernels in this file: srwm_fwd_kernel (register tiles; head sizes up to 16),
+// srwm_fwd_col_kernel (one warp per block W_y / W_q / W_k, whole columns per lane; head sizes
+// 32 and 64), srwm_bwd_kernel (register tiles, reverse time) and srwm_bwd_det_kernel (the
+// gradient with the state detached at every step).  In the tile kernels the three E x E blocks
+// share one register tiling (common.cuh); the small E x 4 block w_b lives transposed in shared
+// memory, one column per designated column group, or -- in the backward -- in registers spread
+// evenly over the lanes.  One block-wide barrier per time step, placed where the softmax needs all
+// of q~ / k~ (forward) or where the row sums of the backward have to cross warps.
 #pragma once
 #include "common.cuh"
 
