@@ -50,6 +50,7 @@ WORKLOADS = {
     # and the grid is a whole number of waves: 592 = 148 SMs x 4, 1184 = 148 x 8)
     "srwm_prof": dict(op="srwm", B=37, H=16, L=512, E=64, dtype="bf16"),
     "delta_prof": dict(op="delta", B=74, H=16, L=1024, E=64, dtype="bf16"),
+    "srwm_prof32": dict(op="srwm", B=111, H=16, L=512, E=32, dtype="f32"),    # 1776 sequences = 148 x 12
 }
 
 # CPU sample sizes for the host baseline (same H, E, dtype=fp32 math; fewer sequences/steps)
