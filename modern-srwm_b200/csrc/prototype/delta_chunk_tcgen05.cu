@@ -3,25 +3,27 @@
 // accumulators in tensor memory -- as a standalone program with its own CPU check.
 //
 //   nvcc -gencode arch=compute_100a,code=sm_100a -O2 -std=c++17 -o delta_chunk_tcgen05 delta_chunk_tcgen05.cu
-//   ./delta_chunk_tcgen05 [sequences] [steps] [bf]      ("bf": inputs rounded to bfloat16 first)
+//   ./delta_chunk_tcgen05 [sequences] [steps]        (inputs are bfloat16, as in the sweep configuration)
 //
 // Per chunk of C = 64 steps and one sequence (one CTA of 128 threads, d = 64), with K, Q, V the
 // chunk's rows, b its gates and W the state at the start of the chunk
 // (recurrence: supervised_learning/fast_weight/__init__.py:186-191):
-//   [P ; O1]  = [K ; Q] W                  (one 128 x 64 x 64 MMA, accumulator D1)
+//   [P ; O1]  = [K ; Q] W                  (128 x 64 x 64 MMA tiles, accumulator D1; W = W_hi + W_lo)
 //   [S1; S2]  = [K ; Q] K^T                (D2)
 //   U         = (I + tril(b S1, -1))^-1 b (V - P)      fp32 forward substitution, one feature column per thread
-//   [VO; O2]  = [tril(S1,-1) ; tril(S2)] U (D3)        v_old = P + VO,  out = O1 + O2,  v_insert = U
+//   [VO; O2]  = [tril(S1,-1) ; tril(S2)] U (D3; U = U_hi + U_lo)    v_old = P + VO, out = O1 + O2, v_insert = U
 //   W^T      += U^T K                      (DW; the state is kept transposed in tensor memory so that the
 //                                           thread that reads row g of it writes row g of the next B operand)
 // All operands are K-major in the canonical no-swizzle shared-memory layout (8-row x 16-byte core
-// matrices); every wait on the MMA completion barrier is bounded and gives up with a status code.
+// matrices).  The MMA truncates fp32 operands to tf32, so W and U are given as two tf32 terms
+// (round-to-nearest high part + remainder).  The chunk's rows arrive through cp.async one chunk
+// ahead.  Every wait on the MMA completion barrier is bounded and gives up with a status code.
 //
-// Status: numerically correct to tf32 accuracy (operands are truncated to 10 mantissa bits by the
-// MMA: out / v_old to ~7e-4, v_insert to ~1e-4 of their scale with bf16 inputs), i.e. not inside the
-// 1e-4 bar of the product kernels without splitting W and U in two tf32 terms; and, as written
-// (operands fetched straight from global memory, a 64-thread solve, one CTA per SM), about three times
-// slower than the shipped sequential kernel.  Kept as the starting point of that row, with its check.
+// Status: v_insert and the final state agree with the fp64 recurrence to 1e-6 / 1e-5 of their scale;
+// out and v_old to 4e-4 (the triangular factors S1, S2 still enter the third product as single tf32
+// terms).  It takes about twice the time of the shipped sequential kernel (3.4 ms against 1.8 ms for
+// 1184 sequences x 2048 steps); the per-phase cycle counts it prints show where: the 64-thread
+// substitution and the scattered operand conversion.  Kept as the starting point of that row.
 #include <cstdio>
 #include <cstdlib>
 #include <cstdint>
@@ -29,6 +31,7 @@
 #include <cmath>
 #include <cstring>
 #include <cuda_runtime.h>
+#include <cuda_bf16.h>
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ uint64_t make_desc(uint32_t saddr) {   // K-major, no swizzle, LBO 128, SBO 2048
@@ -79,18 +82,35 @@ __device__ __forceinline__ bool wait_bar(uint32_t bar, uint32_t parity) {
 }
 
 constexpr int C = 64, E = 64, PADW = 65;
-constexpr int OFF_KQ = 0, OFF_KT = 32768, OFF_WT = 49152, OFF_L = 65536, OFF_UT = 98304, OFF_A = 114688;
-constexpr int OFF_R = OFF_A + C * PADW * 4, SMEM_TOTAL = OFF_R + C * PADW * 4;
+constexpr int OFF_KQ = 0, OFF_KT = 32768, OFF_WT = 49152, OFF_WL = 65536, OFF_L = 81920, OFF_UT = 114688, OFF_UL = 131072,
+              OFF_A = 147456;
+constexpr int OFF_R = OFF_A + C * PADW * 4, OFF_ST = OFF_R + C * PADW * 4 + 128;   // staging: K, Q, V rows (bf16)
+constexpr int ST_BYTES = 3 * C * E * 2, SMEM_TOTAL = OFF_ST + ST_BYTES;
+__device__ __forceinline__ float tf32_hi(float x) { uint32_t r; asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x)); return __uint_as_float(r); }
+__device__ __forceinline__ void cp16(void* d, const void* g) { asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(d)), "l"(g) : "memory"); }
 
 __global__ void __launch_bounds__(128, 1)
-k_chunk(const float* Q, const float* K, const float* V, const float* B, float* W, float* out, float* vold, float* vins,
-        int L, int* status) {
+k_chunk(const __nv_bfloat16* Q, const __nv_bfloat16* K, const __nv_bfloat16* V, const float* B, float* W, float* out,
+        float* vold, float* vins, int L, int* status) {
   extern __shared__ __align__(1024) unsigned char smem[];
   __shared__ __align__(8) uint64_t mbar;
   __shared__ uint32_t tmem_base_s;
   const int tid = threadIdx.x, warp = tid / 32;
   const int n = blockIdx.x;
-  const float* Qn = Q + (size_t)n * L * E; const float* Kn = K + (size_t)n * L * E; const float* Vn = V + (size_t)n * L * E;
+  const __nv_bfloat16* Qn = Q + (size_t)n * L * E; const __nv_bfloat16* Kn = K + (size_t)n * L * E;
+  const __nv_bfloat16* Vn = V + (size_t)n * L * E;
+  __nv_bfloat16* stK = reinterpret_cast<__nv_bfloat16*>(smem + OFF_ST);
+  __nv_bfloat16* stQ = stK + C * E;
+  __nv_bfloat16* stV = stQ + C * E;
+  auto stage = [&](int c) {   // 64 rows x 128 B per tensor, contiguous in global: 512 x 16 B each
+    const int t0 = c * C;
+    for (int i = tid; i < 512; i += 128) {
+      cp16(reinterpret_cast<char*>(stK) + i * 16, reinterpret_cast<const char*>(Kn + (size_t)t0 * E) + i * 16);
+      cp16(reinterpret_cast<char*>(stQ) + i * 16, reinterpret_cast<const char*>(Qn + (size_t)t0 * E) + i * 16);
+      cp16(reinterpret_cast<char*>(stV) + i * 16, reinterpret_cast<const char*>(Vn + (size_t)t0 * E) + i * 16);
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
   const float* Bn = B + (size_t)n * L; float* Wn = W + (size_t)n * E * E;
   float* outn = out + (size_t)n * L * E; float* voldn = vold + (size_t)n * L * E; float* vinsn = vins + (size_t)n * L * E;
   float* sA = reinterpret_cast<float*>(smem + OFF_A);
@@ -113,6 +133,9 @@ k_chunk(const float* Q, const float* K, const float* V, const float* B, float* W
   const uint32_t sbase = smem_u32(smem);
   uint32_t phase = 0;
   bool alive = true;
+  long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  long long tl = clock64();
+#define TICK(i) { long long tn = clock64(); tacc[i] += tn - tl; tl = tn; }
   // W^T into TMEM (row g = column g of W) and into the B operand buffer
   if (tid < 64) {
     float wrow[64];
@@ -120,34 +143,52 @@ k_chunk(const float* Q, const float* K, const float* V, const float* B, float* W
     for (int k = 0; k < 64; ++k) wrow[k] = Wn[k * E + tid];
     tmem_st64(trow + DW, wrow);
 #pragma unroll
-    for (int k4 = 0; k4 < 16; ++k4)
-      *reinterpret_cast<float4*>(smem + OFF_WT + canon(tid, 4 * k4)) = make_float4(wrow[4 * k4], wrow[4 * k4 + 1], wrow[4 * k4 + 2], wrow[4 * k4 + 3]);
+    for (int k4 = 0; k4 < 16; ++k4) {
+      float h[4], l[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) { h[i] = tf32_hi(wrow[4 * k4 + i]); l[i] = wrow[4 * k4 + i] - h[i]; }
+      *reinterpret_cast<float4*>(smem + OFF_WT + canon(tid, 4 * k4)) = make_float4(h[0], h[1], h[2], h[3]);
+      *reinterpret_cast<float4*>(smem + OFF_WL + canon(tid, 4 * k4)) = make_float4(l[0], l[1], l[2], l[3]);
+    }
   }
   const int nchunks = L / C;
+  stage(0);
   for (int c = 0; c < nchunks && alive; ++c) {
     const int t0 = c * C;
     // (1) operands from the chunk's rows
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();
+    TICK(0)
     for (int i = tid; i < C * E; i += 128) {
       const int t = i / E, f = i % E;
-      const float kv = Kn[(size_t)(t0 + t) * E + f], qv = Qn[(size_t)(t0 + t) * E + f];
+      const float kv = __bfloat162float(stK[i]), qv = __bfloat162float(stQ[i]);
       *reinterpret_cast<float*>(smem + OFF_KQ + canon(t, f)) = kv;
       *reinterpret_cast<float*>(smem + OFF_KQ + canon(64 + t, f)) = qv;
       *reinterpret_cast<float*>(smem + OFF_KT + canon(f, t)) = kv;
+    }
+    float vrow[64];          // this thread's V row (token rows only)
+    if (tid < 64) {
+#pragma unroll
+      for (int cc = 0; cc < 64; ++cc) vrow[cc] = __bfloat162float(stV[tid * E + cc]);
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    TICK(1)
     // (2) [P;O1] = [K;Q] W ,  [S1;S2] = [K;Q] K^T
     if (tid == 0) {
       mma_tile(tm + D1, sbase + OFF_KQ, sbase + OFF_WT, false);
+      mma_tile(tm + D1, sbase + OFF_KQ, sbase + OFF_WL, true);
       mma_tile(tm + D2, sbase + OFF_KQ, sbase + OFF_KQ, false);
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
     }
+    if (c + 1 < nchunks) stage(c + 1);   // staging buffer was fully consumed before the barrier above
     if (!wait_bar(bar, phase)) { alive = false; if (tid == 0) status[0] = 1 + c; }
     alive = __syncthreads_and(alive ? 1 : 0) != 0;
     phase ^= 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    TICK(2)
     float keep[64];   // P (token rows) or O1 (query rows)
     if (alive) {
       float s[64];
@@ -157,7 +198,7 @@ k_chunk(const float* Q, const float* K, const float* V, const float* B, float* W
         const int t = tid;
         const float bt = Bn[t0 + t];
 #pragma unroll
-        for (int cc = 0; cc < 64; ++cc) sR[t * PADW + cc] = bt * (Vn[(size_t)(t0 + t) * E + cc] - keep[cc]);
+        for (int cc = 0; cc < 64; ++cc) sR[t * PADW + cc] = bt * (vrow[cc] - keep[cc]);
 #pragma unroll
         for (int ss = 0; ss < 64; ++ss) sA[t * PADW + ss] = ss < t ? bt * s[ss] : 0.f;
 #pragma unroll
@@ -175,49 +216,66 @@ k_chunk(const float* Q, const float* K, const float* V, const float* B, float* W
       }
     }
     __syncthreads();
+    TICK(3)
     // (4) forward substitution, one feature column per thread
     if (alive && tid < 64) {
       const int cc = tid;
       float u[64];
 #pragma unroll
       for (int t = 0; t < 64; ++t) {
-        float acc = sR[t * PADW + cc];
+        float a8[8] = {sR[t * PADW + cc], 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int ss = 0; ss < t; ++ss) acc = fmaf(-sA[t * PADW + ss], u[ss], acc);
-        u[t] = acc;
+        for (int ss = 0; ss < t; ++ss) a8[ss % 8] = fmaf(-sA[t * PADW + ss], u[ss], a8[ss % 8]);
+        u[t] = ((a8[0] + a8[1]) + (a8[2] + a8[3])) + ((a8[4] + a8[5]) + (a8[6] + a8[7]));
       }
 #pragma unroll
       for (int t = 0; t < 64; ++t) vinsn[(size_t)(t0 + t) * E + cc] = u[t];
 #pragma unroll
-      for (int t4 = 0; t4 < 16; ++t4)
-        *reinterpret_cast<float4*>(smem + OFF_UT + canon(cc, 4 * t4)) = make_float4(u[4 * t4], u[4 * t4 + 1], u[4 * t4 + 2], u[4 * t4 + 3]);
+      for (int t4 = 0; t4 < 16; ++t4) {
+        float h[4], l[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { h[i] = tf32_hi(u[4 * t4 + i]); l[i] = u[4 * t4 + i] - h[i]; }
+        *reinterpret_cast<float4*>(smem + OFF_UT + canon(cc, 4 * t4)) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(smem + OFF_UL + canon(cc, 4 * t4)) = make_float4(l[0], l[1], l[2], l[3]);
+      }
     }
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    TICK(4)
     // (5) [VO;O2] = [L1;L2] U ,  W^T += U^T K
     if (tid == 0 && alive) {
       mma_tile(tm + D3, sbase + OFF_L, sbase + OFF_UT, false);
+      mma_tile(tm + D3, sbase + OFF_L, sbase + OFF_UL, true);
       mma_tile(tm + DW, sbase + OFF_UT, sbase + OFF_KT, true);
+      mma_tile(tm + DW, sbase + OFF_UL, sbase + OFF_KT, true);
       asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
     }
     if (alive && !wait_bar(bar, phase)) { alive = false; if (tid == 0) status[0] = 1000 + c; }
     alive = __syncthreads_and(alive ? 1 : 0) != 0;
     phase ^= 1;
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    TICK(5)
     if (alive) {
       float d3[64];
       tmem_ld64(trow + D3, d3);
       if (tid < 64) {
         const int t = tid;
 #pragma unroll
-        for (int cc = 0; cc < 64; ++cc) voldn[(size_t)(t0 + t) * E + cc] = keep[cc] + d3[cc];
+        for (int c4 = 0; c4 < 16; ++c4)
+          *reinterpret_cast<float4*>(voldn + (size_t)(t0 + t) * E + 4 * c4) =
+              make_float4(keep[4 * c4] + d3[4 * c4], keep[4 * c4 + 1] + d3[4 * c4 + 1], keep[4 * c4 + 2] + d3[4 * c4 + 2], keep[4 * c4 + 3] + d3[4 * c4 + 3]);
         float wrow[64];
         tmem_ld64(trow + DW, wrow);
 #pragma unroll
-        for (int k4 = 0; k4 < 16; ++k4)
-          *reinterpret_cast<float4*>(smem + OFF_WT + canon(tid, 4 * k4)) = make_float4(wrow[4 * k4], wrow[4 * k4 + 1], wrow[4 * k4 + 2], wrow[4 * k4 + 3]);
+        for (int k4 = 0; k4 < 16; ++k4) {
+          float h[4], l[4];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) { h[i] = tf32_hi(wrow[4 * k4 + i]); l[i] = wrow[4 * k4 + i] - h[i]; }
+          *reinterpret_cast<float4*>(smem + OFF_WT + canon(tid, 4 * k4)) = make_float4(h[0], h[1], h[2], h[3]);
+          *reinterpret_cast<float4*>(smem + OFF_WL + canon(tid, 4 * k4)) = make_float4(l[0], l[1], l[2], l[3]);
+        }
         if (c == nchunks - 1) {
 #pragma unroll
           for (int k = 0; k < 64; ++k) Wn[k * E + tid] = wrow[k];
@@ -225,13 +283,17 @@ k_chunk(const float* Q, const float* K, const float* V, const float* B, float* W
       } else {
         const int t = tid - 64;
 #pragma unroll
-        for (int cc = 0; cc < 64; ++cc) outn[(size_t)(t0 + t) * E + cc] = keep[cc] + d3[cc];
+        for (int c4 = 0; c4 < 16; ++c4)
+          *reinterpret_cast<float4*>(outn + (size_t)(t0 + t) * E + 4 * c4) =
+              make_float4(keep[4 * c4] + d3[4 * c4], keep[4 * c4 + 1] + d3[4 * c4 + 1], keep[4 * c4 + 2] + d3[4 * c4 + 2], keep[4 * c4 + 3] + d3[4 * c4 + 3]);
       }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    TICK(6)
   }
+  if (tid == 0 && n == 0) for (int i = 0; i < 8; ++i) reinterpret_cast<long long*>(status + 2)[i] = tacc[i];
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tm), "r"(256));
@@ -250,7 +312,7 @@ int main(int argc, char** argv) {
     B[i] = 1.f / (1.f + expf(-2.f * rnd()));
   }
   auto bf = [](float x) { uint32_t u; memcpy(&u, &x, 4); u = (u + 0x7FFF + ((u >> 16) & 1)) & 0xFFFF0000u; float y; memcpy(&y, &u, 4); return y; };
-  if (argc > 3) { for (auto& x : Q) x = bf(x); for (auto& x : K) x = bf(x); for (auto& x : V) x = bf(x); for (auto& x : B) x = bf(x); }
+  { for (auto& x : Q) x = bf(x); for (auto& x : K) x = bf(x); for (auto& x : V) x = bf(x); for (auto& x : B) x = bf(x); }
   for (auto& w : W) w = 0.1f * rnd();
   // reference (double)
   std::vector<double> Wd(W.begin(), W.end());
@@ -262,12 +324,14 @@ int main(int argc, char** argv) {
     for (int r = 0; r < E; ++r) for (int c = 0; c < E; ++c) Wn[r * E + c] += (double)K[o + r] * ins[c];
     for (int c = 0; c < E; ++c) { double s = 0; for (int r = 0; r < E; ++r) s += (double)Q[o + r] * Wn[r * E + c]; r_out[o + c] = (float)s; r_vold[o + c] = (float)vo[c]; r_vins[o + c] = (float)ins[c]; }
   }
-  float *dQ, *dK, *dV, *dB, *dW, *dO, *dVo, *dVi; int* dS;
-  cudaMalloc(&dQ, nl * 4); cudaMalloc(&dK, nl * 4); cudaMalloc(&dV, nl * 4); cudaMalloc(&dB, (size_t)N * L * 4); cudaMalloc(&dW, W.size() * 4);
-  cudaMalloc(&dO, nl * 4); cudaMalloc(&dVo, nl * 4); cudaMalloc(&dVi, nl * 4); cudaMalloc(&dS, 4);
-  cudaMemcpy(dQ, Q.data(), nl * 4, cudaMemcpyHostToDevice); cudaMemcpy(dK, K.data(), nl * 4, cudaMemcpyHostToDevice);
-  cudaMemcpy(dV, V.data(), nl * 4, cudaMemcpyHostToDevice); cudaMemcpy(dB, B.data(), (size_t)N * L * 4, cudaMemcpyHostToDevice);
-  cudaMemcpy(dW, W.data(), W.size() * 4, cudaMemcpyHostToDevice); cudaMemset(dS, 0, 4);
+  float *dB, *dW, *dO, *dVo, *dVi; int* dS; __nv_bfloat16 *dQ, *dK, *dV;
+  cudaMalloc(&dQ, nl * 2); cudaMalloc(&dK, nl * 2); cudaMalloc(&dV, nl * 2); cudaMalloc(&dB, (size_t)N * L * 4); cudaMalloc(&dW, W.size() * 4);
+  std::vector<__nv_bfloat16> hQ(nl), hK(nl), hV(nl);
+  for (size_t i = 0; i < nl; ++i) { hQ[i] = __float2bfloat16(Q[i]); hK[i] = __float2bfloat16(K[i]); hV[i] = __float2bfloat16(V[i]); }
+  cudaMalloc(&dO, nl * 4); cudaMalloc(&dVo, nl * 4); cudaMalloc(&dVi, nl * 4); cudaMalloc(&dS, 128);
+  cudaMemcpy(dQ, hQ.data(), nl * 2, cudaMemcpyHostToDevice); cudaMemcpy(dK, hK.data(), nl * 2, cudaMemcpyHostToDevice);
+  cudaMemcpy(dV, hV.data(), nl * 2, cudaMemcpyHostToDevice); cudaMemcpy(dB, B.data(), (size_t)N * L * 4, cudaMemcpyHostToDevice);
+  cudaMemcpy(dW, W.data(), W.size() * 4, cudaMemcpyHostToDevice); cudaMemset(dS, 0, 128);
   cudaMemset(dO, 0, nl * 4); cudaMemset(dVo, 0, nl * 4); cudaMemset(dVi, 0, nl * 4);
   cudaFuncSetAttribute(k_chunk, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL + 1024);
   cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
@@ -279,6 +343,8 @@ int main(int argc, char** argv) {
   if (e != cudaSuccess) return 0;
   float ms; cudaEventElapsedTime(&ms, e0, e1);
   int st; cudaMemcpy(&st, dS, 4, cudaMemcpyDeviceToHost);
+  long long ta[8]; cudaMemcpy(ta, reinterpret_cast<char*>(dS) + 8, 64, cudaMemcpyDeviceToHost);
+  printf("cycles per chunk (thread 0): wait-stage %lld convert %lld mma1-wait %lld ld+build %lld solve %lld mma2-wait %lld epilogue %lld\n", ta[0] / (L / 64), ta[1] / (L / 64), ta[2] / (L / 64), ta[3] / (L / 64), ta[4] / (L / 64), ta[5] / (L / 64), ta[6] / (L / 64));
   cudaMemcpy(out.data(), dO, nl * 4, cudaMemcpyDeviceToHost); cudaMemcpy(vold.data(), dVo, nl * 4, cudaMemcpyDeviceToHost);
   cudaMemcpy(vins.data(), dVi, nl * 4, cudaMemcpyDeviceToHost); cudaMemcpy(W.data(), dW, W.size() * 4, cudaMemcpyDeviceToHost);
   auto relmax = [](const std::vector<float>& a, const std::vector<float>& b) { double me = 0, mr = 0; for (size_t i = 0; i < a.size(); ++i) { me = fmax(me, fabs((double)a[i] - b[i])); mr = fmax(mr, fabs((double)b[i])); } return me / mr; };
