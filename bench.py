@@ -7,19 +7,27 @@
 
 A "step" is one forward + backward pass of the operator over the (rank-local shard of the)
 workload's batch, followed by the reduction of the per-sample state gradients into the
-slow-weight gradient bucket and, for N > 1, its NCCL all-reduce.  The default workload is
-the scale-sweep configuration: SRWM, B=1024 (global, batch-sharded over the ranks), H=16,
-d_head=64, L=2048, bf16 activations, fp32 state.  The same run also times the delta-rule
-configuration of the sweep (B=512, H=16, d=64, L=8192) and reports it under "delta".
+slow-weight gradient bucket and, for N > 1, its NCCL all-reduce (enqueued behind the
+reduction and overlapped with the next step's forward).  The default workload is the
+scale-sweep configuration: SRWM, B=1024 (global, batch-sharded over the ranks), H=16,
+d_head=64, L=2048, bf16 activations, fp32 state, run through the layer-level entry points with
+the slow weights un-repeated ([1,H,d,.], batch stride 0).  The same run also times the
+delta-rule configuration of the sweep (B=512, H=16, d=64, L=8192) and reports it under "delta".
 
 Rank 0 prints ONE JSON line.  ``value`` is whole-job tokens/s (B*L / step time, max over
 ranks) with the inputs resident in HBM; ``e2e`` is the same metric through the public
 autograd entry point (``self_ref_v0``) with the activations starting in pinned host memory
-and the slow-weight gradients read back to the host every step.
+and the slow-weight gradients read back to the host every step.  ``roofline`` is the HBM
+view of the dominant kernel (the metric asks for it), ``roofline_fp32`` its CUDA-core fp32
+view (the ceiling that binds); ``parity_spot`` compares two sequences of the last timed step
+with the float64 oracle; ``small_configs`` times the two small reference configurations.
 
 ``--impl reference`` times the reference math (its per-step PyTorch loop with autograd,
-restated in oracle/srwm_oracle.py) on the host CPU cores, on a bounded sample of the same
-workload; rank 0 only.
+restated in oracle/srwm_oracle.py) on the host CPU cores, on a bounded sample of the
+workload (the line's ``config`` names the sample); rank 0 only.  When a GPU and the
+reference's own CUDA extensions (built unmodified into oracle/_ref) are present, that arm
+also times those kernels inside their valid envelope and reports them under
+``ref_cuda_kernels``.
 """
 from __future__ import annotations
 
@@ -51,6 +59,10 @@ WORKLOADS = {
     "srwm_prof": dict(op="srwm", B=37, H=16, L=512, E=64, dtype="bf16"),
     "delta_prof": dict(op="delta", B=74, H=16, L=1024, E=64, dtype="bf16"),
     "srwm_prof32": dict(op="srwm", B=111, H=16, L=512, E=32, dtype="f32"),    # 1776 sequences = 148 x 12
+    # the layer-level kernels on the same capture sizes: layer forward (input softmax, shift state,
+    # reset mask) + detached-state backward; packed delta forward + backward
+    "srwm_layer_prof": dict(op="srwm_layer", B=37, H=16, L=512, E=64, dtype="bf16"),
+    "delta_layer_prof": dict(op="delta_packed", B=74, H=16, L=1024, E=64, dtype="bf16"),
 }
 
 # CPU sample sizes for the host baseline (same H, E, dtype=fp32 math; fewer sequences/steps)
@@ -61,14 +73,19 @@ def algorithmic_bytes(op, E, s, per="fwd+bwd"):
     """Bytes per (sequence, step) that the operator must move (s = bytes per activation
     element), and bytes per sequence for the state."""
     D = 3 * E + 4
-    if op == "srwm":
+    if op in ("srwm", "srwm_layer"):
         fwd = E * s + E * s + (5 * E + 8) * 4              # x read, y write, saved write
         bwd = 2 * E * s + E * s + (5 * E + 8) * 4          # x, dy read, dx write, saved read
         st_f, st_b = 2 * E * D * 4, 2 * E * D * 4          # W0 read + W_L write ; W_L read + dW write
+        if op == "srwm_layer":                             # detached backward: k, y_diff, beta; W_y only
+            bwd = 2 * E * s + E * s + (2 * E + 4) * 4
+            st_f, st_b = 3 * E * D * 4, 3 * E * E * 4
     else:
         fwd = (3 * E + 1) * s + E * s + 2 * E * 4          # q,k,v,beta read, out write, v_old/v_ins write
         bwd = (3 * E + 1) * s + E * s + (3 * E + 1) * s + 2 * E * 4
         st_f, st_b = 2 * E * E * 4, 2 * E * E * 4
+        if op == "delta_packed":
+            st_f = E * E * 4                               # zero-initialised state is not read
     if per == "fwd":
         return fwd, st_f
     if per == "bwd":
@@ -79,8 +96,18 @@ def algorithmic_bytes(op, E, s, per="fwd+bwd"):
 def algorithmic_flops(op, E):
     """Flops per (sequence, step), forward and backward (FMA = 2)."""
     D = 3 * E + 4
+    if op == "srwm_layer":
+        return 6 * E * D, 6 * E * E
     n = E * D if op == "srwm" else E * E
     return 6 * n, 14 * n
+
+
+# CUDA-core fp32 ceiling: SMs x fp32 lanes per SM x 2 flops per FMA x clock
+N_SM, FP32_LANES = 148, 128
+
+
+def fp32_peak_tflops(sm_mhz):
+    return N_SM * FP32_LANES * 2 * sm_mhz * 1e6 / 1e12
 
 
 def load_peaks():
@@ -189,6 +216,59 @@ def cpu_baseline(wl, runs=3):
                       f"L={s['L']} d={wl['E']} ({t:.1f} s per pass)"}
 
 
+def ref_cuda_kernel_timings(steps=20, warmup=5):
+    """The reference's own CUDA kernels (oracle/_ref: its two .cu files compiled unmodified for
+    sm_100a) forward+backward on cuda:0, on the two configurations inside their valid envelope
+    (SRWM d_head 16 within one time chunk; delta rule d 64).  Zero-filled outputs are allocated
+    per call exactly as the reference's autograd functions do.  Reference-arm only."""
+    if not torch.cuda.is_available():
+        return {"unavailable": "no CUDA device in this process"}
+    sys.path.insert(0, os.path.join(ROOT, "oracle"))
+    import ref_kernels as ref
+    if not ref.available():
+        return {"unavailable": "oracle/_ref not built (needs the upstream sources at build time)"}
+    dev = torch.device("cuda", 0)
+    res = {}
+    for name in ("srwm_c1", "delta_c2"):
+        wl = WORKLOADS[name]
+        B, H, L, E = wl["B"], wl["H"], wl["L"], wl["E"]
+        g = torch.Generator(device=dev).manual_seed(11)
+        rn = lambda *s: torch.randn(*s, device=dev, generator=g)
+        if wl["op"] == "srwm":
+            x, go = rn(B, H, L, E), rn(B, H, L, E)
+            std = E ** -0.5
+            W0 = [rn(B, H, E, E) * std for _ in range(3)] + [rn(B, H, E, 4) * std]
+            W = [w.clone() for w in W0]
+
+            def run():
+                for a_, b_ in zip(W, W0):
+                    a_.copy_(b_)
+                _, saved = ref.srwm_forward(x, *W)
+                ref.srwm_backward(x, saved, go, *W)
+        else:
+            Q, K = torch.softmax(rn(B, H, L, E), -1), torch.softmax(rn(B, H, L, E), -1)
+            V, Bt, go = rn(B, H, L, E), torch.sigmoid(rn(B, H, L, 1)), rn(B, H, L, E)
+            W = torch.zeros(B, H, E, E, device=dev)
+
+            def run():
+                W.zero_()
+                _, saved = ref.delta_forward(Q, K, V, Bt, W)
+                ref.delta_backward(Q, K, V, Bt, saved, go, W)
+        for _ in range(warmup):
+            run()
+        torch.cuda.synchronize(dev)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            run()
+        e1.record()
+        torch.cuda.synchronize(dev)
+        ms = e0.elapsed_time(e1) / steps
+        res[name] = {"config": config_of(name, wl, 1)["workload"], "ms_per_step": ms,
+                     "tokens_per_s": B * L / (ms * 1e-3)}
+    return res
+
+
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -204,12 +284,25 @@ def run_reference(args):
     val = s["B"] * s["L"] / t
     sample = (f"{wl['op']} fwd+bwd, reference per-step PyTorch loop + autograd on the host CPU, fp32, "
               f"B={s['B']} H={wl['H']} L={s['L']} d={wl['E']}")
+    # the configuration this arm RAN: a bounded sample of the workload (fewer sequences and steps,
+    # same heads and head size), converted to tokens/s
+    cfg = {"workload": f"{args.workload} scaled to a CPU sample: {wl['op']} fwd+bwd B={s['B']} H={wl['H']} "
+                       f"L={s['L']} d_head={wl['E']} fp32 on {cores} host cores (full workload: B={wl['B']} "
+                       f"L={wl['L']} {wl['dtype']} activations)",
+           "scaled": True, "global_batch": s["B"], "seq_len": s["L"], "heads": wl["H"], "d_head": wl["E"],
+           "full_workload": config_of(args.workload, wl, args.gpus)["workload"],
+           "parallelism": "host CPU threads", "l2": "n/a (CPU)"}
     line = {"impl": "reference", "metric": "SRWM/delta fwd+bwd tokens/s", "value": val, "unit": "tokens/s",
             "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": t * 1e3,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-            "data": "synthetic", "config": config_of(args.workload, wl, args.gpus),
+            "data": "synthetic", "config": cfg,
             "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    if not args.no_ref_cuda:
+        try:
+            line["ref_cuda_kernels"] = ref_cuda_kernel_timings()
+        except Exception as exc:   # the CPU line must still be printed
+            line["ref_cuda_kernels"] = {"unavailable": f"{type(exc).__name__}: {exc}"[:200]}
     print(json.dumps(line), flush=True)
 
 
@@ -217,7 +310,10 @@ def config_of(name, wl, n):
     return {"workload": f"{name}: {wl['op']} fwd+bwd B={wl['B']} H={wl['H']} L={wl['L']} d_head={wl['E']} "
                         f"{wl['dtype']} activations, fp32 state",
             "global_batch": wl["B"], "seq_len": wl["L"], "heads": wl["H"], "d_head": wl["E"],
-            "parallelism": f"batch-sharded x{n}", "l2": "inputs_exceed_l2"}
+            "parallelism": f"batch-sharded x{n}" + ("; slow weights un-repeated [1,H,d,.], per-sample gradients "
+                                                     "batch-reduced into one flat bucket, one NCCL all-reduce per step"
+                                                     if wl["op"].startswith("srwm") else ""),
+            "l2": "inputs_exceed_l2"}
 
 
 # ---------------------------------------------------------------------------------------
@@ -229,29 +325,40 @@ class OpBench:
 
     def __init__(self, wl, Bl, device, seed):
         import srwm_b200 as sb
+        from srwm_b200 import layer_ops
         from srwm_b200.dist import GradBucket
-        self.sb, self.wl, self.Bl, self.dev = sb, wl, Bl, device
+        self.sb, self.lo, self.wl, self.Bl, self.dev = sb, layer_ops, wl, Bl, device
         H, L, E = wl["H"], wl["L"], wl["E"]
         dt = torch.bfloat16 if wl["dtype"] == "bf16" else torch.float32
         self.dt = dt
         g = torch.Generator(device=device).manual_seed(seed)
         rn = lambda *s: torch.randn(*s, device=device, dtype=torch.float32, generator=g)
         self.launches_per_step = 0
-        if wl["op"] == "srwm":
+        self.bucket = None
+        op = wl["op"]
+        if op in ("srwm", "srwm_layer"):
             self.x = self._big_randn((Bl, H, L, E), g, dt)
             self.go = self._big_randn((Bl, H, L, E), g, dt)
             std = E ** -0.5
+            # the slow weights stay [1,H,d,.]: the kernels read them with a batch stride of zero
             self.slow = [rn(1, H, E, E) * std for _ in range(3)] + [rn(1, H, E, 4) * std]
-            self.state = [torch.empty(Bl, H, E, w.shape[-1], device=device) for w in self.slow]
             self.bucket = GradBucket([w.shape[1:] for w in self.slow], device)
-        else:
+            if op == "srwm_layer":
+                self.shift = [0.05 * std * rn(Bl, H, E, w.shape[-1]) for w in self.slow]
+                self.done = torch.rand(Bl, L, device=device, generator=g) < 0.01
+        elif op == "delta":
             self.Q = self._big_randn((Bl, H, L, E), g, dt, softmax=True)
             self.K = self._big_randn((Bl, H, L, E), g, dt, softmax=True)
             self.V = self._big_randn((Bl, H, L, E), g, dt)
             self.Bt = torch.sigmoid(rn(Bl, H, L, 1)).to(dt)
             self.go = self._big_randn((Bl, H, L, E), g, dt)
             self.W = torch.zeros(Bl, H, E, E, device=device)
-            self.bucket = None
+        else:   # delta_packed: the layers' raw slow-net rows [q | k | v | b], time-major
+            RS = 3 * E + 1
+            raw = self._big_randn((L, Bl, H * RS), g, dt)
+            self.rows = raw.view(L, Bl, H, RS).permute(1, 2, 0, 3)
+            self.go = self._big_randn((Bl, H, L, E), g, dt)
+            self.W = torch.empty(Bl, H, E, E, device=device)
         self.ev = []
 
     @staticmethod
@@ -268,24 +375,37 @@ class OpBench:
         return out
 
     def step(self, timed=False):
-        sb = self.sb
+        sb, lo = self.sb, self.lo
         rec = None
         if timed:
             rec = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        if self.wl["op"] == "srwm":
-            for s, w in zip(self.state, self.slow):
-                s.copy_(w.expand_as(s))
+        op = self.wl["op"]
+        if op == "srwm":
             if rec: rec[0].record()
-            out, saved = sb.srwm_forward(self.x, *self.state)
+            out, shift_out, saved = lo.srwm_layer_forward(self.x, self.slow, None, None, input_softmax=False)
             if rec: rec[1].record()
-            grads = sb.srwm_backward(self.x, saved, self.go, *self.state)
+            grads = lo.srwm_layer_backward(self.x, saved, self.go, self.slow, shift_out, None, input_softmax=False)
             if rec: rec[2].record()
+            # batch sum of the per-sample dL/dW_0 straight into the flat bucket, then its all-reduce
+            # behind it (asynchronous: it overlaps the next step's forward)
+            self.bucket.wait()
             for i in range(4):
                 self.bucket.reduce_into(i, grads[1 + i])
-            self.bucket.all_reduce()
+            self.bucket.all_reduce(async_op=True)
             self.last = (out, grads[0])
             self.launches_per_step = 2 + 4
-        else:
+        elif op == "srwm_layer":
+            if rec: rec[0].record()
+            out, shift_out, saved = lo.srwm_layer_forward(self.x, self.slow, self.shift, self.done, True)
+            if rec: rec[1].record()
+            gx, gWy = lo.srwm_backward_detached(self.x, saved, self.go, self.slow[0], self.shift[0], self.done, True)
+            if rec: rec[2].record()
+            self.bucket.wait()
+            self.bucket.reduce_into(0, gWy)
+            self.bucket.all_reduce(async_op=True)
+            self.last = (out, gx)
+            self.launches_per_step = 2 + 1
+        elif op == "delta":
             self.W.zero_()
             if rec: rec[0].record()
             out, saved = sb.delta_forward(self.Q, self.K, self.V, self.Bt, self.W)
@@ -294,19 +414,71 @@ class OpBench:
             if rec: rec[2].record()
             self.last = (out, grads[0])
             self.launches_per_step = 2
+        else:
+            if rec: rec[0].record()
+            out, saved = lo.delta_packed_forward(self.rows, self.W, 0.0, True)
+            if rec: rec[1].record()
+            g = lo.delta_packed_backward(self.rows, saved, self.go, self.W, 0.0)
+            if rec: rec[2].record()
+            self.last = (out, g[0] if isinstance(g, (tuple, list)) else g)
+            self.launches_per_step = 2
         if rec:
             self.ev.append(rec)
+
+    def finish(self):
+        """Inside the timed region, after the last step: the pending all-reduce must have landed."""
+        if self.bucket is not None:
+            self.bucket.wait()
 
     def kernel_ms(self):
         f = [a.elapsed_time(b) for a, b, _ in self.ev]
         b = [b_.elapsed_time(c) for _, b_, c in self.ev]
         return sum(f) / len(f), sum(b) / len(b)
 
+    def parity_spot(self):
+        """Two sequences of the last timed step against the float64 oracle (reverse-time recipe on
+        the CPU): max|err| / max|ref| of the forward output and of grad_x.  The streamed tensors are
+        bf16 in the sweep configurations, so the bound is bf16 rounding (8e-3), not 1e-4."""
+        sys.path.insert(0, os.path.join(ROOT, "oracle"))
+        import srwm_oracle as orc
+        wl = self.wl
+        if wl["op"] not in ("srwm", "delta"):
+            return None
+        Bl, H = self.Bl, wl["H"]
+        picks = sorted({(0, 0), (Bl - 1, H - 1)})
+        out, gx = self.last
+        fwd_err = grad_err = 0.0
+        for n, h in picks:
+            sl = (slice(n, n + 1), slice(h, h + 1))
+            c = lambda t: t[sl].detach().double().cpu()
+            if wl["op"] == "srwm":
+                W0 = [w[:, h:h + 1].double().cpu() for w in self.slow]
+                f = orc.srwm_forward_explicit(c(self.x), *W0)
+                r = orc.srwm_backward_explicit(c(self.x), f["q"], f["k"], f["beta"], f["y_diff"], f["q_diff"],
+                                               f["k_diff"], f["beta_diff"], c(self.go), f["W_y"], f["W_q"],
+                                               f["W_k"], f["w_b"])
+                ref_out, ref_g = f["out"], r[0]
+            else:
+                E = wl["E"]
+                f = orc.delta_forward_explicit(c(self.Q), c(self.K), c(self.V), c(self.Bt),
+                                               torch.zeros(1, 1, E, E, dtype=torch.float64))
+                r = orc.delta_backward_explicit(c(self.Q), c(self.K), c(self.V), c(self.Bt), f["v_old"],
+                                                f["v_insert"], c(self.go), f["W"])
+                ref_out, ref_g = f["out"], r[0]
+            fwd_err = max(fwd_err, orc.rel_max(c(out), ref_out))
+            grad_err = max(grad_err, orc.rel_max(c(gx), ref_g))
+        tol = 8e-3 if wl["dtype"] == "bf16" else 1e-3
+        return {"fwd": fwd_err, "grad": grad_err, "sequences": [list(p) for p in picks],
+                "metric": "max|err| / max|ref| against the float64 oracle", "tolerance": tol,
+                "ok": bool(fwd_err < tol and grad_err < tol)}
 
-def timed_region(fn, steps, warmup, dist_on, device):
+
+def timed_region(fn, steps, warmup, dist_on, device, finish=None):
     import torch.distributed as dist
     for _ in range(warmup):
         fn(False)
+    if finish:
+        finish()
     torch.cuda.synchronize(device)
     if dist_on:
         dist.barrier()
@@ -315,6 +487,8 @@ def timed_region(fn, steps, warmup, dist_on, device):
     e0.record()
     for _ in range(steps):
         fn(True)
+    if finish:
+        finish()
     e1.record()
     torch.cuda.synchronize(device)
     if dist_on:
@@ -424,6 +598,42 @@ def run_e2e(wl, Bl, device, steps, warmup, dist_on):
     return ms, h2d, d2h
 
 
+def small_config_timings(device, steps=20, warmup=5):
+    """Forward+backward through the plain operator calls at the two small reference
+    configurations (the ones the reference's own CUDA kernels are valid at)."""
+    res = {}
+    for name in ("srwm_c1", "delta_c2"):
+        wl = WORKLOADS[name]
+        B, H, L, E = wl["B"], wl["H"], wl["L"], wl["E"]
+        import srwm_b200 as sb
+        g = torch.Generator(device=device).manual_seed(11)
+        rn = lambda *s: torch.randn(*s, device=device, generator=g)
+        if wl["op"] == "srwm":
+            x, go = rn(B, H, L, E), rn(B, H, L, E)
+            std = E ** -0.5
+            W0 = [rn(B, H, E, E) * std for _ in range(3)] + [rn(B, H, E, 4) * std]
+            W = [w.clone() for w in W0]
+
+            def run(_t):
+                for a_, b_ in zip(W, W0):
+                    a_.copy_(b_)
+                _, saved = sb.srwm_forward(x, *W)
+                sb.srwm_backward(x, saved, go, *W)
+        else:
+            Q, K = torch.softmax(rn(B, H, L, E), -1), torch.softmax(rn(B, H, L, E), -1)
+            V, Bt, go = rn(B, H, L, E), torch.sigmoid(rn(B, H, L, 1)), rn(B, H, L, E)
+            W = torch.zeros(B, H, E, E, device=device)
+
+            def run(_t):
+                W.zero_()
+                _, saved = sb.delta_forward(Q, K, V, Bt, W)
+                sb.delta_backward(Q, K, V, Bt, saved, go, W)
+        ms = timed_region(run, steps, warmup, False, device)
+        res[name] = {"config": config_of(name, wl, 1)["workload"], "ms_per_step": ms,
+                     "tokens_per_s": B * L / (ms * 1e-3)}
+    return res
+
+
 def run_ours(args):
     import torch.distributed as dist
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -442,7 +652,7 @@ def run_ours(args):
     results = {}
     clocks = None
     names = [args.workload] + ([] if args.no_delta or args.workload != "srwm_c5" else ["delta_c5"])
-    hbm_peak, peak_kind, _ = load_peaks()
+    hbm_peak, peak_kind, sm_max_mhz = load_peaks()
     for name in names:
         wl = WORKLOADS[name]
         lo, hi = shard_range(wl["B"], n, rank)
@@ -451,17 +661,17 @@ def run_ours(args):
         sampler = ClockSampler(local_rank) if (rank == 0 and name == names[0]) else None
         if sampler:
             sampler.start()
-        ms = timed_region(ob.step, args.steps, args.warmup, dist_on, device)
+        ms = timed_region(ob.step, args.steps, args.warmup, dist_on, device, finish=ob.finish)
         if sampler:
             clocks = sampler.stop()
         fwd_ms, bwd_ms = ob.kernel_ms()
         launches = ob.launches_per_step * args.steps
+        spot = ob.parity_spot() if (rank == 0 and n == 1 and not args.no_cpu) else None
         del ob
         torch.cuda.empty_cache()
         e2e_ms, h2d, d2h = (None, 0, 0)
-        if not args.no_e2e:
-            e2e_ms, h2d, d2h = run_e2e(wl, Bl, device, max(1, min(args.steps, args.e2e_steps)), max(1, min(args.warmup, 3)),
-                                       dist_on)
+        if not args.no_e2e and wl["op"] in ("srwm", "delta"):
+            e2e_ms, h2d, d2h = run_e2e(wl, Bl, device, max(1, args.steps), max(1, min(args.warmup, 3)), dist_on)
             torch.cuda.empty_cache()
         tokens = wl["B"] * wl["L"]
         s = 2 if wl["dtype"] == "bf16" else 4
@@ -470,19 +680,29 @@ def run_ours(args):
         bwd_bytes = seqs_local * (wl["L"] * per_step + per_seq)
         ff, fb = algorithmic_flops(wl["op"], wl["E"])
         achieved = bwd_bytes / (bwd_ms * 1e-3) / 1e9
+        bwd_tf = seqs_local * wl["L"] * fb / (bwd_ms * 1e-3) / 1e12
+        fwd_tf = seqs_local * wl["L"] * ff / (fwd_ms * 1e-3) / 1e12
+        peak32 = fp32_peak_tflops(sm_max_mhz)
+        kname = {"srwm": "srwm_bwd_kernel", "srwm_layer": "srwm_bwd_det_kernel", "delta": "delta_bwd_kernel",
+                 "delta_packed": "delta_bwd_kernel<PACKED>"}[wl["op"]]
         results[name] = dict(
-            wl=wl, ms=ms, tokens_per_s=tokens / (ms * 1e-3), fwd_ms=fwd_ms, bwd_ms=bwd_ms, launches=launches,
+            wl=wl, ms=ms, tokens_per_s=tokens / (ms * 1e-3), fwd_ms=fwd_ms, bwd_ms=bwd_ms, launches=launches, spot=spot,
             e2e=None if e2e_ms is None else {"value": tokens / (e2e_ms * 1e-3), "unit": "tokens/s",
                                              "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                                             "ms_per_step": e2e_ms},
-            roofline={"bound": "hbm", "kernel": f"{wl['op']}_bwd_kernel", "achieved": achieved, "peak": hbm_peak,
+                                             "ms_per_step": e2e_ms, "steps": max(1, args.steps)},
+            # HBM view of the dominant kernel (the metric asks for it).  What binds this kernel is
+            # CUDA-core fp32 issue (64-77 flop/B), reported as roofline_fp32.
+            roofline={"bound": "fp32_issue", "kernel": kname, "achieved": achieved, "peak": hbm_peak,
                       "unit": "GB/s", "frac": achieved / hbm_peak, "peak_source": f"of {peak_kind}",
                       "traffic": (NCU_BWD_DRAM_BYTES_PER_SEQ_STEP[wl["op"]] * seqs_local * wl["L"]
-                                  if wl["E"] == 64 and wl["dtype"] == "bf16" else None),
+                                  if wl["E"] == 64 and wl["dtype"] == "bf16" and wl["op"] in NCU_BWD_DRAM_BYTES_PER_SEQ_STEP
+                                  else None),
                       "algorithmic_bytes_per_launch": bwd_bytes, "launch_ms": bwd_ms},
-            fp32={"fwd_tflops": seqs_local * wl["L"] * ff / (fwd_ms * 1e-3) / 1e12,
-                  "bwd_tflops": seqs_local * wl["L"] * fb / (bwd_ms * 1e-3) / 1e12,
-                  "note": "algorithmic flops / kernel time; CUDA-core fp32 peak is 148 SMs x 128 lanes x 2 x clock"})
+            roofline_fp32={"bound": "fp32_issue", "kernel": kname, "achieved": bwd_tf, "peak": peak32,
+                           "unit": "TFLOP/s", "frac": bwd_tf / peak32,
+                           "peak_source": f"{N_SM} SMs x {FP32_LANES} lanes x 2 x {sm_max_mhz:.0f} MHz (nominal CUDA-core fp32)",
+                           "fwd_kernel": {"achieved": fwd_tf, "frac": fwd_tf / peak32, "launch_ms": fwd_ms},
+                           "algorithmic_flops_per_launch": seqs_local * wl["L"] * fb})
     if rank == 0:
         main = results[names[0]]
         wl = main["wl"]
@@ -490,21 +710,29 @@ def run_ours(args):
                 "n_gpus": n, "steps": args.steps, "warmup": args.warmup, "ms_per_step": main["ms"],
                 "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "f32 state / " + wl["dtype"] + " activations", "data": "synthetic",
-                "config": config_of(names[0], wl, n), "roofline": main["roofline"], "fp32": main["fp32"],
+                "config": config_of(names[0], wl, n), "roofline": main["roofline"],
+                "roofline_fp32": main["roofline_fp32"],
                 "kernel_ms": {"fwd": main["fwd_ms"], "bwd": main["bwd_ms"]},
                 "gpu_launches": main["launches"], "clocks": clocks}
         if main["e2e"] is not None:
             line["e2e"] = main["e2e"]
-        if n == 1 and not args.no_cpu:
+        if main["spot"] is not None:
+            line["parity_spot"] = main["spot"]
+        if n == 1 and not args.no_cpu and wl["op"] in CPU_SAMPLE:
             line["cpu_baseline"] = cpu_baseline(wl)
         for extra in names[1:]:
             r = results[extra]
             line["delta"] = {"value": r["tokens_per_s"], "unit": "tokens/s", "ms_per_step": r["ms"],
-                             "config": config_of(extra, r["wl"], n), "roofline": r["roofline"], "fp32": r["fp32"],
+                             "config": config_of(extra, r["wl"], n), "roofline": r["roofline"],
+                             "roofline_fp32": r["roofline_fp32"],
                              "kernel_ms": {"fwd": r["fwd_ms"], "bwd": r["bwd_ms"]}, "gpu_launches": r["launches"],
                              "e2e": r["e2e"]}
+            if r["spot"] is not None:
+                line["delta"]["parity_spot"] = r["spot"]
             if n == 1 and not args.no_cpu:
                 line["delta"]["cpu_baseline"] = cpu_baseline(r["wl"])
+        if n == 1 and args.workload == "srwm_c5" and not args.no_small:
+            line["small_configs"] = small_config_timings(device)
         print(json.dumps(line), flush=True)
     if dist_on:
         dist.barrier()
@@ -799,129 +1027,6 @@ def run_layer_table(args):
          {"tokens": L_ * B})
 
 
-def run_layer_prof(args):
-    """The layer-level kernels on a capture-sized workload (activations > L2, a whole number of
-    waves), for profiler runs: `srwm` = layer forward (input softmax, un-repeated slow weights,
-    shift state, reset mask) + detached-state backward, B=37 H=16 L=512 d=64 bf16; `delta` =
-    packed forward + packed backward, B=74 H=16 L=1024 d=64 bf16.  One JSON line with the
-    CUDA-event time of each kernel and its algorithmic bytes."""
-    from srwm_b200 import layer_ops as lo
-    device = torch.device("cuda", 0)
-    torch.cuda.set_device(device)
-    g = torch.Generator(device=device).manual_seed(5)
-    H, E = 16, 64
-    hbm_peak, peak_kind, _ = load_peaks()
-    if args.layer_prof == "srwm":
-        B, L_ = 37, 512
-        x = OpBench._big_randn((B, H, L_, E), g, torch.bfloat16)
-        go = OpBench._big_randn((B, H, L_, E), g, torch.bfloat16)
-        std = E ** -0.5
-        base = [torch.randn(1, H, E, E, device=device, generator=g) * std for _ in range(3)]
-        base.append(torch.randn(1, H, E, 4, device=device, generator=g) * std)
-        shift = [0.05 * std * torch.randn(B, H, E, w.shape[-1], device=device, generator=g) for w in base]
-        done = torch.rand(B, L_, device=device, generator=g) < 0.01
-        names = ("srwm_fwd_col_kernel<EXT>", "srwm_bwd_det_kernel")
-        fbytes = B * H * (L_ * (2 * E * 2 + (5 * E + 8) * 4) + 3 * E * (3 * E + 4) * 4)
-        bbytes = B * H * (L_ * (3 * E * 2 + (2 * E + 4) * 4) + 3 * E * E * 4)
-
-        def fwd():
-            return lo.srwm_layer_forward(x, base, shift, done, True)
-
-        def bwd(res):
-            return lo.srwm_backward_detached(x, res[2], go, base[0], shift[0], done, True)
-    else:
-        B, L_ = 74, 1024
-        RS = 3 * E + 1
-        raw = OpBench._big_randn((L_, B, H * RS), g, torch.bfloat16)
-        rows = raw.view(L_, B, H, RS).permute(1, 2, 0, 3)
-        go = OpBench._big_randn((B, H, L_, E), g, torch.bfloat16)
-        W = torch.empty(B, H, E, E, device=device)
-        names = ("delta_fwd_col_kernel<PACKED>", "delta_bwd_kernel<PACKED>")
-        fbytes = B * H * (L_ * (RS * 2 + E * 2 + 2 * E * 4) + E * E * 4)
-        bbytes = B * H * (L_ * (2 * RS * 2 + E * 2 + 2 * E * 4) + 2 * E * E * 4)
-
-        def fwd():
-            return lo.delta_packed_forward(rows, W, 0.0, True)
-
-        def bwd(res):
-            return lo.delta_packed_backward(rows, res[1], go, W, 0.0)
-    tf, tb = [], []
-    for i in range(args.warmup + args.steps):
-        e = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-        e[0].record()
-        res = fwd()
-        e[1].record()
-        bwd(res)
-        e[2].record()
-        torch.cuda.synchronize(device)
-        if i >= args.warmup:
-            tf.append(e[0].elapsed_time(e[1]))
-            tb.append(e[1].elapsed_time(e[2]))
-    f, b = sum(tf) / len(tf), sum(tb) / len(tb)
-    print(json.dumps({"workload": f"{args.layer_prof}_layer_prof", "sequences": B * H, "steps_per_sequence": L_,
-                      "kernels": {names[0]: {"ms": f, "algorithmic_bytes": fbytes, "GB/s": fbytes / f / 1e6,
-                                             "frac_of_hbm_peak": fbytes / f / 1e6 / hbm_peak},
-                                  names[1]: {"ms": b, "algorithmic_bytes": bbytes, "GB/s": bbytes / b / 1e6,
-                                             "frac_of_hbm_peak": bbytes / b / 1e6 / hbm_peak}},
-                      "peak_source": f"of {peak_kind}"}), flush=True)
-
-
-def run_chunkwise_probe(args):
-    """Feasibility measurement for a chunkwise (UT-transform) delta-rule forward on tensor cores: the
-    chunk recursion written with torch batched matmuls (cuBLAS; chunk 64, fp32 triangular solve) at
-    three operand precisions, against this library's sequential kernel -- accuracy of the fp32
-    saved tensor v_insert and wall time.  A measurement aid, not a product path."""
-    import srwm_b200 as sb
-    device = torch.device("cuda", 0)
-    torch.cuda.set_device(device)
-    N, H, L_, E, C = 64, 16, 2048, 64, 64
-    g = torch.Generator(device=device).manual_seed(1)
-    Q = torch.softmax(torch.randn(N, H, L_, E, device=device, generator=g), -1).bfloat16()
-    K = torch.softmax(torch.randn(N, H, L_, E, device=device, generator=g), -1).bfloat16()
-    V = torch.randn(N, H, L_, E, device=device, generator=g).bfloat16()
-    Bt = torch.sigmoid(torch.randn(N, H, L_, 1, device=device, generator=g)).bfloat16()
-    W = torch.zeros(N, H, E, E, device=device)
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    sb.delta_forward(Q, K, V, Bt, W)
-    W.zero_()
-    e0.record()
-    _, saved = sb.delta_forward(Q, K, V, Bt, W)
-    e1.record()
-    torch.cuda.synchronize(device)
-    seq_ms = e0.elapsed_time(e1)
-    ins_ref = saved[1]
-    eye = torch.eye(C, device=device)
-
-    def chunkwise(mm_dtype, tf32):
-        torch.backends.cuda.matmul.allow_tf32 = tf32
-        mm = (lambda a, b: a @ b) if mm_dtype is None else (lambda a, b: (a.to(mm_dtype) @ b.to(mm_dtype)).float())
-        Wc = torch.zeros(N, H, E, E, device=device)
-        ins = []
-        for c in range(L_ // C):
-            sl = slice(c * C, (c + 1) * C)
-            q, k, v, b = (t[:, :, sl].float() for t in (Q, K, V, Bt))
-            A = torch.tril(b * mm(k, k.transpose(-1, -2)), -1)
-            U = torch.linalg.solve_triangular(eye + A, b * (v - mm(k, Wc)), upper=False)
-            _ = mm(q, Wc) + mm(torch.tril(mm(q, k.transpose(-1, -2))), U)
-            Wc = Wc + mm(k.transpose(-1, -2), U)
-            ins.append(U)
-        return torch.cat(ins, 2)
-
-    res = {}
-    for name, dt, tf in (("fp32", None, False), ("tf32", None, True), ("bf16", torch.bfloat16, False)):
-        for _ in range(2):
-            torch.cuda.synchronize(device)
-            t0 = time.perf_counter()
-            u = chunkwise(dt, tf)
-            torch.cuda.synchronize(device)
-            t1 = time.perf_counter()
-        res[name] = {"v_insert_max_rel_err": float((u - ins_ref).abs().max() / ins_ref.abs().max()),
-                     "cublas_composition_ms": (t1 - t0) * 1e3}
-    torch.backends.cuda.matmul.allow_tf32 = False
-    print(json.dumps({"workload": f"delta forward, {N * H} sequences x {L_} steps, d=64, bf16 streams, chunk {C}",
-                      "sequential_kernel_ms": seq_ms, "chunkwise": res}), flush=True)
-
-
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -932,20 +1037,14 @@ def main():
     ap.add_argument("--no-delta", action="store_true", help="skip the delta-rule sweep configuration")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-cpu", action="store_true")
-    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-small", action="store_true", help="skip the timings of the two small configurations")
+    ap.add_argument("--no-ref-cuda", action="store_true",
+                    help="reference arm: do not time the reference's own CUDA kernels")
     ap.add_argument("--table", action="store_true", help="operator-level timings of every configuration")
     ap.add_argument("--layer-table", action="store_true",
                     help="layer-level timings: fused layer call vs torch ops around the operator")
-    ap.add_argument("--layer-prof", choices=["srwm", "delta"], default=None,
-                    help="layer-level kernels on a capture-sized workload (for profiler runs)")
-    ap.add_argument("--chunkwise-probe", action="store_true",
-                    help="accuracy / time of a chunkwise delta forward written with library matmuls")
     args = ap.parse_args()
-    if args.chunkwise_probe:
-        run_chunkwise_probe(args)
-    elif args.layer_prof:
-        run_layer_prof(args)
-    elif args.layer_table:
+    if args.layer_table:
         run_layer_table(args)
     elif args.table:
         run_table(args)

@@ -579,7 +579,7 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
     return reinterpret_cast<float*>(in_buf(b) + SM::QKV_BYTES + T * SM::ROW_IO + 2 * T * SM::ROW_F);
   };
 
-  {
+  if (nchunks > 0) {   // (an empty sequence has nothing to stage: W_0 = W_L, dL/dW_0 = 0)
     const int c0 = nchunks - 1;
     stage_chunk(c0);
     cp_async_commit();

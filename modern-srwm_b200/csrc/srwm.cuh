@@ -860,7 +860,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
     stage_rows<16, P>(bb, p.beta.row(n, h, t0), p.beta.sl, nt, tid);
     stage_rows<16, P>(bb + T * 16, p.bd.row(n, h, t0), p.bd.sl, nt, tid);
   };
-  stage_chunk(nchunks - 1);
+  if (nchunks > 0) stage_chunk(nchunks - 1);   // (an empty sequence has nothing to stage: dL/dW_0 = dL/dW_L)
   cp_async_commit();
 
   int par = 0;
