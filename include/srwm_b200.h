@@ -24,6 +24,9 @@
  *     validated before any CUDA call, so invalid calls are rejected on machines without
  *     a GPU as well.  N*H*L == 0 is a successful no-op.
  *   - Supported head dimensions: E in {8, 16, 32, 64} (delta rule: M == E).
+ *   - Device: the kernels are launched on the calling thread's CURRENT CUDA device, which must be
+ *     the device that owns every pointer of the call and the stream (call cudaSetDevice first;
+ *     the Python layer does).  The library never changes the current device.
  */
 #ifndef SRWM_B200_H_
 #define SRWM_B200_H_
@@ -90,7 +93,9 @@ typedef struct srwm_b200_srwm_fwd_args {
   int32_t N, H, L, E;
   int32_t io_dtype;
   uint32_t flags;
-  int32_t variant;                  /* 0 = default kernel configuration */
+  int32_t variant;                  /* 0 = the library chooses the kernel configuration (by head size and by
+                                       how N*H sequences fill the GPU); ids >= 1 name one compiled
+                                       configuration and are always honoured (srwm_b200_num_variants) */
   int32_t reserved;
   srwm_b200_seq   x;                /* in  [N,H,L,E] io_dtype */
   srwm_b200_state W_y, W_q, W_k;    /* in/out [N,H,E,E] */
@@ -311,16 +316,24 @@ int srwm_b200_reduce_batch(const float* src, int64_t stride_n, int32_t N, int64_
 /* ---- queries (no CUDA call is made by these) ---- */
 int         srwm_b200_abi_version(void);
 int         srwm_b200_head_dim_supported(int32_t E);           /* 1 / 0 */
-int         srwm_b200_num_variants(int32_t op, int32_t E);     /* op: 0 srwm_fwd 1 srwm_bwd
+int         srwm_b200_num_variants(int32_t op, int32_t E);     /* valid variant values are 0 .. this-1.
+                                                                  op: 0 srwm_fwd 1 srwm_bwd
                                                                   2 delta_fwd 3 delta_bwd
                                                                   4 srwm_bwd_detached */
 const char* srwm_b200_strerror(int code);
 int         srwm_b200_last_cuda_error(void);   /* cudaError_t of the last failed call of the
                                                   calling thread, 0 if none */
 /* Describes the kernel configuration a call would use (threads per sequence, rows per
- * thread, time-chunk length, dynamic shared memory bytes): writes "P R T smem" into out. */
+ * thread, time-chunk length, dynamic shared memory bytes): writes "P R T smem" into out.
+ * With variant 0 this is the configuration of a grid that fills the GPU. */
 int         srwm_b200_describe(int32_t op, int32_t E, int32_t io_dtype, int32_t variant,
                                int32_t out[4]);
+/* The same for a given number of sequences (grid = N*H) on a GPU with num_sms multiprocessors
+ * (<= 0: 148): writes "P R T smem id" into out, id being the configuration that variant 0 resolves
+ * to.  (A delta-rule backward call whose last wave would be partial runs its whole waves on one
+ * configuration and the remainder on another; the one of the whole waves is reported.) */
+int         srwm_b200_describe_for_grid(int32_t op, int32_t E, int32_t io_dtype, int32_t variant,
+                                        int64_t grid, int32_t num_sms, int32_t out[5]);
 
 #ifdef __cplusplus
 }

@@ -107,48 +107,61 @@ const char* srwm_b200_strerror(int code) {
   }
 }
 
-int srwm_b200_describe(int32_t op, int32_t E, int32_t io_dtype, int32_t variant, int32_t out[4]) {
+int srwm_b200_describe_for_grid(int32_t op, int32_t E, int32_t io_dtype, int32_t variant, int64_t grid,
+                                int32_t num_sms, int32_t out[5]) {
   if (!out) return SRWM_B200_ERR_NULL;
   if (io_dtype != SRWM_B200_F32 && io_dtype != SRWM_B200_BF16) return SRWM_B200_ERR_DTYPE;
-  srwm::KernelInfo info = {0, 0, 0, 0};
+  if (grid < 0 || grid > 0x7fffffffLL) return SRWM_B200_ERR_SHAPE;
+  srwm::KernelInfo info = {0, 0, 0, 0, 0};
   int ce = 0, rc;
   const bool bf = io_dtype == SRWM_B200_BF16;
+  const int g = (int)grid, sms = num_sms > 0 ? num_sms : srwm::DEFAULT_SMS;
   switch (op) {
     case srwm::OP_SRWM_FWD: {
       srwm::SrwmFwdParams p = {};
-      rc = bf ? srwm::dispatch_srwm_fwd_bf16(E, variant, p, 0, 0, &info, 1, &ce)
-              : srwm::dispatch_srwm_fwd_f32(E, variant, p, 0, 0, &info, 1, &ce);
+      rc = bf ? srwm::dispatch_srwm_fwd_bf16(E, variant, p, g, 0, &info, 1, &ce, sms)
+              : srwm::dispatch_srwm_fwd_f32(E, variant, p, g, 0, &info, 1, &ce, sms);
       break;
     }
     case srwm::OP_SRWM_BWD: {
       srwm::SrwmBwdParams p = {};
-      rc = bf ? srwm::dispatch_srwm_bwd_bf16(E, variant, p, 0, 0, &info, 1, &ce)
-              : srwm::dispatch_srwm_bwd_f32(E, variant, p, 0, 0, &info, 1, &ce);
+      rc = bf ? srwm::dispatch_srwm_bwd_bf16(E, variant, p, g, 0, &info, 1, &ce, sms)
+              : srwm::dispatch_srwm_bwd_f32(E, variant, p, g, 0, &info, 1, &ce, sms);
       break;
     }
     case srwm::OP_SRWM_BWD_DET: {
       srwm::SrwmBwdDetParams p = {};
-      rc = bf ? srwm::dispatch_srwm_bwd_det_bf16(E, variant, p, 0, 0, &info, 1, &ce)
-              : srwm::dispatch_srwm_bwd_det_f32(E, variant, p, 0, 0, &info, 1, &ce);
+      rc = bf ? srwm::dispatch_srwm_bwd_det_bf16(E, variant, p, g, 0, &info, 1, &ce, sms)
+              : srwm::dispatch_srwm_bwd_det_f32(E, variant, p, g, 0, &info, 1, &ce, sms);
       break;
     }
     case srwm::OP_DELTA_FWD: {
       srwm::DeltaFwdParams p = {};
-      rc = bf ? srwm::dispatch_delta_fwd_bf16(E, variant, p, 0, 0, &info, 1, &ce)
-              : srwm::dispatch_delta_fwd_f32(E, variant, p, 0, 0, &info, 1, &ce);
+      rc = bf ? srwm::dispatch_delta_fwd_bf16(E, variant, p, g, 0, &info, 1, &ce, sms)
+              : srwm::dispatch_delta_fwd_f32(E, variant, p, g, 0, &info, 1, &ce, sms);
       break;
     }
     case srwm::OP_DELTA_BWD: {
       srwm::DeltaBwdParams p = {};
-      rc = bf ? srwm::dispatch_delta_bwd_bf16(E, variant, p, 0, 0, &info, 1, &ce)
-              : srwm::dispatch_delta_bwd_f32(E, variant, p, 0, 0, &info, 1, &ce);
+      rc = bf ? srwm::dispatch_delta_bwd_bf16(E, variant, p, g, 0, &info, 1, &ce, sms)
+              : srwm::dispatch_delta_bwd_f32(E, variant, p, g, 0, &info, 1, &ce, sms);
       break;
     }
     default:
       return SRWM_B200_ERR_SHAPE;
   }
   if (rc != 0) return finish(rc, ce);
-  out[0] = info.P; out[1] = info.R; out[2] = info.T; out[3] = info.smem;
+  out[0] = info.P; out[1] = info.R; out[2] = info.T; out[3] = info.smem; out[4] = info.id;
+  return 0;
+}
+
+int srwm_b200_describe(int32_t op, int32_t E, int32_t io_dtype, int32_t variant, int32_t out[4]) {
+  if (!out) return SRWM_B200_ERR_NULL;
+  int32_t o5[5];
+  // a grid large enough to fill any GPU: the configuration of full waves
+  const int rc = srwm_b200_describe_for_grid(op, E, io_dtype, variant, 1 << 20, 0, o5);
+  if (rc != 0) return rc;
+  out[0] = o5[0]; out[1] = o5[1]; out[2] = o5[2]; out[3] = o5[3];
   return 0;
 }
 
@@ -205,8 +218,8 @@ int srwm_b200_srwm_layer_forward(const srwm_b200_srwm_fwd_args* a, const srwm_b2
   p.Wy = view(a->W_y); p.Wq = view(a->W_q); p.Wk = view(a->W_k); p.wb = view(a->w_b);
   int ce = 0;
   const int rc = a->io_dtype == SRWM_B200_BF16
-                     ? srwm::dispatch_srwm_fwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
-                     : srwm::dispatch_srwm_fwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+                     ? srwm::dispatch_srwm_fwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0)
+                     : srwm::dispatch_srwm_fwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0);
   return finish(rc, ce);
 }
 
@@ -249,8 +262,8 @@ int srwm_b200_srwm_layer_backward(const srwm_b200_srwm_bwd_args* a, const srwm_b
   p.gWy = view(a->grad_W_y); p.gWq = view(a->grad_W_q); p.gWk = view(a->grad_W_k); p.gwb = view(a->grad_w_b);
   int ce = 0;
   const int rc = a->io_dtype == SRWM_B200_BF16
-                     ? srwm::dispatch_srwm_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
-                     : srwm::dispatch_srwm_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+                     ? srwm::dispatch_srwm_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0)
+                     : srwm::dispatch_srwm_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0);
   return finish(rc, ce);
 }
 
@@ -282,8 +295,8 @@ int srwm_b200_srwm_backward_detached(const srwm_b200_srwm_bwd_detached_args* a, 
   p.done = a->done; p.done_sn = a->done_stride_n; p.done_sl = a->done_stride_l;
   int ce = 0;
   const int rc = a->io_dtype == SRWM_B200_BF16
-                     ? srwm::dispatch_srwm_bwd_det_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
-                     : srwm::dispatch_srwm_bwd_det_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+                     ? srwm::dispatch_srwm_bwd_det_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0)
+                     : srwm::dispatch_srwm_bwd_det_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0);
   return finish(rc, ce);
 }
 
@@ -310,8 +323,8 @@ int srwm_b200_delta_forward(const srwm_b200_delta_fwd_args* a, void* stream) {
   p.W = view(a->W);
   int ce = 0;
   const int rc = a->io_dtype == SRWM_B200_BF16
-                     ? srwm::dispatch_delta_fwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
-                     : srwm::dispatch_delta_fwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+                     ? srwm::dispatch_delta_fwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0)
+                     : srwm::dispatch_delta_fwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0);
   return finish(rc, ce);
 }
 
@@ -343,8 +356,8 @@ int srwm_b200_delta_backward(const srwm_b200_delta_bwd_args* a, void* stream) {
   p.W = view(a->W); p.gW0 = view(a->grad_W0);
   int ce = 0;
   const int rc = a->io_dtype == SRWM_B200_BF16
-                     ? srwm::dispatch_delta_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
-                     : srwm::dispatch_delta_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+                     ? srwm::dispatch_delta_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0)
+                     : srwm::dispatch_delta_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0);
   return finish(rc, ce);
 }
 
@@ -373,8 +386,8 @@ int srwm_b200_delta_packed_forward(const srwm_b200_delta_packed_fwd_args* a, voi
   p.W = view(a->W);
   int ce = 0;
   const int rc = a->io_dtype == SRWM_B200_BF16
-                     ? srwm::dispatch_delta_fwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
-                     : srwm::dispatch_delta_fwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+                     ? srwm::dispatch_delta_fwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0)
+                     : srwm::dispatch_delta_fwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0);
   return finish(rc, ce);
 }
 
@@ -404,8 +417,8 @@ int srwm_b200_delta_packed_backward(const srwm_b200_delta_packed_bwd_args* a, vo
   p.W = view(a->W); p.gW0 = view(a->grad_W0);
   int ce = 0;
   const int rc = a->io_dtype == SRWM_B200_BF16
-                     ? srwm::dispatch_delta_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce)
-                     : srwm::dispatch_delta_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce);
+                     ? srwm::dispatch_delta_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0)
+                     : srwm::dispatch_delta_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0);
   return finish(rc, ce);
 }
 

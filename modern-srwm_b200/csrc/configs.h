@@ -1,87 +1,134 @@
-// Compiled kernel configurations: X(E, variant, P, R, T, PK, MINB)
+// Compiled kernel configurations.
+//
+// Variant ids.  In every argument block `variant` 0 means "let the library choose" (by head size,
+// and by how the grid of sequences fills the GPU); every compiled configuration also has an explicit
+// id >= 1 that is always honoured, so that configurations can be timed against each other through
+// the same ABI.  The ids of one (operator, head size) are contiguous from 1.  The configurations the
+// automatic choice can pick are always compiled; the remaining ones are tuning alternatives and are
+// compiled only with -DSRWM_TUNING_VARIANTS (csrc/build.py --tuning).
+//
+// Register-tile kernels: X(E, id, P, R, T, PK, MINB, LAYER)
 //   E      head dimension            P     threads per sequence (= CTA size)
 //   R      state rows per thread     T     time steps staged per chunk
 //   PK     packed fma.rn.f32x2 (1) or scalar fma (0)
 //   MINB   CTAs per SM the register allocation is bounded for (__launch_bounds__)
-// Variant 0 is what the library uses by default; the others exist so that alternative
-// tilings can be timed against each other through the same ABI.
+//   LAYER  1: the layer-level form of the call (input softmax, base + shift state, reset flags;
+//          packed rows for the delta rule) is instantiated for this configuration too
 #pragma once
 
-#define SRWM_FWD_CONFIGS(X)      \
-  X(8, 0, 32, 2, 16, true, 8)    \
-  X(16, 0, 32, 4, 16, true, 8)   \
-  X(16, 1, 32, 2, 16, true, 8)   \
-  X(32, 1, 64, 8, 16, true, 6)   \
-  X(32, 2, 32, 8, 16, true, 8)   \
-  X(32, 3, 64, 4, 16, true, 6)   \
-  X(64, 1, 128, 8, 16, true, 3)  \
-  X(64, 2, 128, 16, 16, true, 3) \
-  X(64, 3, 128, 8, 16, false, 3)
+#ifdef SRWM_TUNING_VARIANTS
+#define SRWM_TUNING(...) __VA_ARGS__
+#else
+#define SRWM_TUNING(...)
+#endif
 
-// Column-layout forward (96 threads, one warp per block): Y(E, variant, T, PK, MINB, DPRE, NRP)
+// ---- SRWM forward -------------------------------------------------------------------------------
+#define SRWM_FWD_CONFIGS(X)              \
+  X(8, 1, 32, 2, 16, true, 8, 1)         \
+  X(16, 1, 32, 4, 16, true, 8, 1)        \
+  SRWM_TUNING(                           \
+  X(16, 2, 32, 2, 16, true, 8, 0)        \
+  X(32, 2, 64, 8, 16, true, 6, 0)        \
+  X(32, 3, 32, 8, 16, true, 8, 0)        \
+  X(32, 4, 64, 4, 16, true, 6, 0)        \
+  X(64, 2, 128, 8, 16, true, 3, 0)       \
+  X(64, 3, 128, 16, 16, true, 3, 0)      \
+  X(64, 4, 128, 8, 16, false, 3, 0))
+
+// Column-layout forward (96 threads, one warp per block): Y(E, id, T, PK, MINB, DPRE, NRP, LAYER)
 //   DPRE  the k warp publishes q-k once per step (two-warp named barrier) instead of every
 //         thread recomputing it in the second pass
 //   NRP   row parts per column group (1 = whole columns per lane)
-#define SRWM_FWD_COL_CONFIGS(Y)     \
-  Y(64, 0, 16, true, 4, true, 1)    \
-  Y(64, 4, 16, true, 4, false, 1)   \
-  Y(64, 5, 16, true, 4, true, 2)    \
-  Y(64, 6, 16, true, 4, true, 4)    \
-  Y(64, 7, 16, false, 4, true, 2)   \
-  Y(64, 8, 16, true, 3, true, 2)    \
-  Y(16, 2, 16, true, 8, true, 2)    \
-  Y(16, 3, 16, true, 16, true, 2)   \
-  Y(32, 0, 16, true, 8, true, 2)    \
-  Y(32, 4, 16, true, 8, false, 1)   \
-  Y(32, 5, 16, true, 8, true, 1)    \
-  Y(32, 6, 16, true, 8, true, 4)    \
-  Y(32, 7, 16, true, 12, true, 4)
+#define SRWM_FWD_COL_CONFIGS(Y)          \
+  Y(32, 1, 16, true, 8, true, 2, 1)      \
+  Y(64, 1, 16, true, 4, true, 1, 1)      \
+  SRWM_TUNING(                           \
+  Y(16, 3, 16, true, 8, true, 2, 0)      \
+  Y(16, 4, 16, true, 16, true, 2, 0)     \
+  Y(32, 5, 16, true, 8, false, 1, 0)     \
+  Y(32, 6, 16, true, 8, true, 1, 0)      \
+  Y(32, 7, 16, true, 8, true, 4, 0)      \
+  Y(32, 8, 16, true, 12, true, 4, 0)     \
+  Y(64, 5, 16, true, 4, false, 1, 0)     \
+  Y(64, 6, 16, true, 4, true, 2, 0)      \
+  Y(64, 7, 16, true, 4, true, 4, 0)      \
+  Y(64, 8, 16, false, 4, true, 2, 0)     \
+  Y(64, 9, 16, true, 3, true, 2, 0))
 
-#define SRWM_BWD_CONFIGS(X)      \
-  X(8, 0, 32, 2, 16, true, 8)    \
-  X(16, 0, 32, 2, 16, true, 8)   \
-  X(16, 1, 32, 4, 16, true, 8)   \
-  X(32, 0, 64, 4, 16, true, 6)   \
-  X(32, 1, 64, 8, 16, true, 6)   \
-  X(32, 2, 32, 8, 16, true, 8)   \
-  X(64, 0, 128, 8, 16, true, 2)  \
-  X(64, 1, 256, 8, 16, true, 1)  \
-  X(64, 2, 128, 8, 16, false, 2)
+// ---- SRWM backward ------------------------------------------------------------------------------
+#define SRWM_BWD_CONFIGS(X)              \
+  X(8, 1, 32, 2, 16, true, 8, 1)         \
+  X(16, 1, 32, 2, 16, true, 8, 1)        \
+  X(32, 1, 64, 4, 16, true, 6, 1)        \
+  SRWM_TUNING(                           \
+  X(16, 2, 32, 4, 16, true, 8, 0)        \
+  X(32, 2, 64, 8, 16, true, 6, 0)        \
+  X(32, 3, 32, 8, 16, true, 8, 0)        \
+  X(64, 2, 128, 8, 16, true, 2, 1)       \
+  X(64, 3, 256, 8, 16, true, 1, 0)       \
+  X(64, 4, 128, 8, 16, false, 2, 0))
 
-// Backward with the state detached at every step (W_y and its gradient only)
-#define SRWM_BWD_DET_CONFIGS(X)  \
-  X(8, 0, 32, 2, 16, true, 8)    \
-  X(16, 0, 32, 4, 16, true, 8)   \
-  X(32, 0, 64, 8, 16, true, 6)   \
-  X(64, 0, 128, 16, 16, true, 4)
+// Second formulation of the backward (srwm_bwd2.cuh): Z(E, id, P, R, T, MINB, OPT); always serves the
+// layer-level form as well
+#define SRWM_BWD2_CONFIGS(Z)             \
+  Z(64, 1, 128, 8, 16, 2, 0)             \
+  SRWM_TUNING(                           \
+  Z(32, 4, 64, 4, 16, 5, 0)              \
+  Z(32, 5, 64, 4, 8, 6, 0)               \
+  Z(64, 5, 128, 8, 16, 2, 1)             \
+  Z(64, 6, 128, 8, 16, 2, 2)             \
+  Z(64, 7, 128, 8, 16, 2, 3))
 
-#define DELTA_FWD_CONFIGS(X)     \
-  X(8, 0, 32, 2, 16, true, 8)    \
-  X(16, 0, 32, 4, 16, true, 8)   \
-  X(32, 0, 32, 8, 16, true, 12)  \
-  X(32, 1, 64, 8, 16, true, 8)   \
-  X(64, 6, 64, 16, 8, true, 8)   \
-  X(64, 1, 64, 32, 8, true, 8)   \
-  X(64, 2, 64, 64, 8, true, 8)   \
-  X(64, 3, 128, 16, 8, true, 6)  \
-  X(64, 4, 32, 16, 8, true, 10)  \
-  X(64, 5, 64, 16, 8, false, 8)
+// Backward with the state detached at every step (W_y and its gradient only): X(E, id, P, R, T, PK, MINB)
+#define SRWM_BWD_DET_CONFIGS(X)          \
+  X(8, 1, 32, 2, 16, true, 8)            \
+  X(16, 1, 32, 4, 16, true, 8)           \
+  X(32, 1, 64, 8, 16, true, 6)           \
+  X(64, 1, 128, 16, 16, true, 4)
 
-// Column-layout delta forward: Y(E, variant, P, T, PK, MINB, NRP); the default at E = 64
-#define DELTA_FWD_COL_CONFIGS(Y)  \
-  Y(64, 0, 32, 8, true, 8, 1)     \
-  Y(64, 7, 32, 8, true, 8, 2)     \
-  Y(64, 8, 64, 8, true, 7, 2)     \
-  Y(32, 2, 32, 16, true, 16, 1)   \
-  Y(32, 3, 32, 16, true, 16, 2)
+// ---- delta rule forward -------------------------------------------------------------------------
+// At E = 64 the automatic choice is the column kernel: id 1 (one warp per sequence) when the grid fills
+// the GPU, id 3 (four warps per sequence) when there are so few sequences that a lone warp's step
+// latency is exposed; the packed (layer-level) form uses id 1 / id 4.
+#define DELTA_FWD_CONFIGS(X)             \
+  X(8, 1, 32, 2, 16, true, 8, 1)         \
+  X(16, 1, 32, 4, 16, true, 8, 1)        \
+  X(32, 1, 32, 8, 16, true, 12, 1)       \
+  X(64, 4, 64, 16, 8, true, 8, 1)        \
+  SRWM_TUNING(                           \
+  X(32, 2, 64, 8, 16, true, 8, 0)        \
+  X(64, 5, 64, 32, 8, true, 8, 0)        \
+  X(64, 6, 64, 64, 8, true, 8, 0)        \
+  X(64, 7, 128, 16, 8, true, 6, 0)       \
+  X(64, 8, 32, 16, 8, true, 10, 0)       \
+  X(64, 9, 64, 16, 8, false, 8, 0))
 
-#define DELTA_BWD_CONFIGS(X)     \
-  X(8, 0, 32, 2, 16, true, 8)    \
-  X(16, 0, 32, 4, 16, true, 8)   \
-  X(32, 0, 32, 8, 16, true, 10)  \
-  X(32, 1, 64, 8, 16, true, 8)   \
-  X(64, 0, 64, 8, 8, true, 4)    \
-  X(64, 1, 128, 8, 8, true, 4)   \
-  X(64, 2, 128, 16, 8, true, 4)  \
-  X(64, 3, 64, 16, 8, true, 4)   \
-  X(64, 4, 64, 8, 8, false, 4)
+// Column-layout delta forward: Y(E, id, P, T, PK, MINB, NRP, LAYER, UNR)   UNR: unrolling of the step loop
+#define DELTA_FWD_COL_CONFIGS(Y)         \
+  Y(64, 1, 32, 8, true, 8, 1, 1, 1)      \
+  Y(64, 2, 64, 8, true, 7, 2, 0, 1)      \
+  Y(64, 3, 128, 16, true, 4, 2, 0, 2)    \
+  SRWM_TUNING(                           \
+  Y(32, 3, 32, 16, true, 16, 1, 0, 1)    \
+  Y(32, 4, 32, 16, true, 16, 2, 0, 1)    \
+  Y(64, 10, 32, 8, true, 8, 2, 0, 1)     \
+  Y(64, 11, 64, 8, true, 8, 1, 0, 1)     \
+  Y(64, 12, 128, 8, true, 4, 2, 0, 1)    \
+  Y(64, 13, 128, 32, true, 3, 2, 0, 2))
+
+// ---- delta rule backward ------------------------------------------------------------------------
+// At E = 64: id 1 (64 threads per sequence) on whole waves; id 2 (128) for the sequences of a partial
+// last wave and for small grids.
+#define DELTA_BWD_CONFIGS(X)             \
+  X(8, 1, 32, 2, 16, true, 8, 1)         \
+  X(16, 1, 32, 4, 16, true, 8, 1)        \
+  X(32, 1, 32, 8, 16, true, 10, 1)       \
+  X(64, 1, 64, 8, 8, true, 4, 1)         \
+  X(64, 2, 128, 8, 8, true, 4, 0)        \
+  SRWM_TUNING(                           \
+  X(32, 2, 64, 8, 16, true, 8, 0)        \
+  X(64, 3, 256, 8, 8, true, 2, 0)        \
+  X(64, 4, 128, 16, 8, true, 4, 0)       \
+  X(64, 5, 64, 16, 8, true, 4, 0)        \
+  X(64, 6, 64, 8, 8, false, 4, 0)        \
+  X(64, 7, 256, 4, 8, true, 2, 0))

@@ -27,6 +27,7 @@ constexpr unsigned F_PACKED = 8u, F_ZERO_INIT = 16u;
 struct DeltaFwdParams {
   int N, H, L;
   unsigned flags;
+  int seq0;   // first sequence of this launch (a call may be split into launches of different configurations)
   SeqView Q, K, V, beta, out, v_old, v_ins;   // Q doubles as the packed rows
   StateView W;
   float eps;
@@ -35,6 +36,7 @@ struct DeltaFwdParams {
 struct DeltaBwdParams {
   int N, H, L;
   unsigned flags;
+  int seq0;   // first sequence of this launch
   SeqView Q, K, V, beta, v_old, v_ins, gout, gQ, gK, gV, gbeta;   // Q / gQ double as the packed rows
   StateView W, gW0;
   float eps;
@@ -123,7 +125,8 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
   constexpr int NRG = TL::NRG, C = TL::C, R2 = R / 2;
   const int tid = threadIdx.x;
   const int rg = tid % NRG, cg = tid / NRG;
-  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
+  const int seq = blockIdx.x + p.seq0;
+  const int n = seq / p.H, h = seq % p.H;
   const bool save = !(p.flags & 1u);
 
   extern __shared__ __align__(16) unsigned char smem[];
@@ -314,17 +317,19 @@ struct DeltaFwdColSmem {
   static constexpr int TOTAL = 2 * IN_BYTES + CONV_BYTES + OUT_BYTES;
 };
 
-template <typename TIO, int E, int P, int T, bool PK, int MINB, int NRP, bool PACKED = false>
+template <typename TIO, int E, int P, int T, bool PK, int MINB, int NRP, bool PACKED = false, int UNR = 1>
 __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdParams p) {
   using SM = DeltaFwdColSmem<TIO, E, T, PACKED>;
   using TS = typename std::conditional<PACKED, float, TIO>::type;   // element type of the staged v rows
   constexpr int CPL = (E * NRP) / P, RL = E / NRP, RL2 = RL / 2;
+  constexpr int NA = (CPL == 1 && RL >= 16) ? 4 : 2;   // accumulator chains per column
   static_assert(NRP == 1 || NRP == 2, "row parts per column group");
   static_assert(P % 32 == 0 && CPL >= 1 && CPL * P == E * NRP && RL % 4 == 0, "bad column-layout shape");
   const int lane = threadIdx.x;   // thread index within the sequence's P threads
   constexpr int LPP = 32 / NRP;   // lanes per row part within a warp
   const int rp = (lane % 32) / LPP, c0 = ((lane / 32) * LPP + lane % LPP) * CPL;
-  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
+  const int seq = blockIdx.x + p.seq0;
+  const int n = seq / p.H, h = seq % p.H;
   const bool save = !(p.flags & 1u);
 
   extern __shared__ __align__(16) unsigned char smem[];
@@ -416,22 +421,26 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdPa
       sb = beta_buf(c & 1);
     }
 
-#pragma unroll 1
+#pragma unroll UNR
     for (int t = 0; t < nt; ++t) {
       const float4* k4 = reinterpret_cast<const float4*>(sk + t * E);
       const float4* q4 = reinterpret_cast<const float4*>(sq + t * E);
       // ---- pass A: v_old = k.W on this lane's columns ------------------------------------
-      u64 a0[CPL], a1[CPL];
+      // (NA independent accumulator chains per column: with one column per lane two chains of
+      // RL/4 dependent FMAs would leave the lane waiting on its own results)
+      u64 acc[NA][CPL];
 #pragma unroll
-      for (int cc = 0; cc < CPL; ++cc) { a0[cc] = 0ull; a1[cc] = 0ull; }
+      for (int a = 0; a < NA; ++a)
+#pragma unroll
+        for (int cc = 0; cc < CPL; ++cc) acc[a][cc] = 0ull;
 #pragma unroll
       for (int e4 = 0; e4 < RL / 4; ++e4) {
         const float4 kv = k4[e4 * NRP + rp];
         const u64 k0 = pack2(kv.x, kv.y), k1 = pack2(kv.z, kv.w);
 #pragma unroll
         for (int cc = 0; cc < CPL; ++cc) {
-          a0[cc] = fma2<PK>(k0, W[2 * e4][cc], a0[cc]);
-          a1[cc] = fma2<PK>(k1, W[2 * e4 + 1][cc], a1[cc]);
+          acc[(2 * e4) % NA][cc] = fma2<PK>(k0, W[2 * e4][cc], acc[(2 * e4) % NA][cc]);
+          acc[(2 * e4 + 1) % NA][cc] = fma2<PK>(k1, W[2 * e4 + 1][cc], acc[(2 * e4 + 1) % NA][cc]);
         }
       }
       float vc[CPL], vold[CPL], ins[CPL];
@@ -440,11 +449,13 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdPa
       u64 ins2[CPL];
 #pragma unroll
       for (int cc = 0; cc < CPL; ++cc) {
-        vold[cc] = allreduce_parts<NRP>(hsum2(a0[cc]) + hsum2(a1[cc]));
+        float part = hsum2(acc[0][cc]) + hsum2(acc[1][cc]);
+        if constexpr (NA == 4) part += hsum2(acc[2][cc]) + hsum2(acc[3][cc]);
+        vold[cc] = allreduce_parts<NRP>(part);
         ins[cc] = bt * (vc[cc] - vold[cc]);
         ins2[cc] = dup2(ins[cc]);
-        a0[cc] = 0ull;
-        a1[cc] = 0ull;
+#pragma unroll
+        for (int a = 0; a < NA; ++a) acc[a][cc] = 0ull;
       }
       // ---- pass B: W += k^T ins, out = q.W (updated) --------------------------------------
 #pragma unroll
@@ -457,13 +468,17 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdPa
         for (int cc = 0; cc < CPL; ++cc) {
           W[2 * e4][cc] = fma2<PK>(k0, ins2[cc], W[2 * e4][cc]);
           W[2 * e4 + 1][cc] = fma2<PK>(k1, ins2[cc], W[2 * e4 + 1][cc]);
-          a0[cc] = fma2<PK>(q0, W[2 * e4][cc], a0[cc]);
-          a1[cc] = fma2<PK>(q1, W[2 * e4 + 1][cc], a1[cc]);
+          acc[(2 * e4) % NA][cc] = fma2<PK>(q0, W[2 * e4][cc], acc[(2 * e4) % NA][cc]);
+          acc[(2 * e4 + 1) % NA][cc] = fma2<PK>(q1, W[2 * e4 + 1][cc], acc[(2 * e4 + 1) % NA][cc]);
         }
       }
       float o[CPL];
 #pragma unroll
-      for (int cc = 0; cc < CPL; ++cc) o[cc] = allreduce_parts<NRP>(hsum2(a0[cc]) + hsum2(a1[cc]));
+      for (int cc = 0; cc < CPL; ++cc) {
+        float part = hsum2(acc[0][cc]) + hsum2(acc[1][cc]);
+        if constexpr (NA == 4) part += hsum2(acc[2][cc]) + hsum2(acc[3][cc]);
+        o[cc] = allreduce_parts<NRP>(part);
+      }
       if (rp == 0) {
         st_vec<CPL>(so + t * E + c0, o);
         if (save) {
@@ -534,7 +549,8 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
   const int rg = tid % NRG, cg = tid / NRG;
   const int warp = tid / 32, lane = tid % 32;
   const int cgl = lane / NRG;
-  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
+  const int seq = blockIdx.x + p.seq0;
+  const int n = seq / p.H, h = seq % p.H;
 
   extern __shared__ __align__(16) unsigned char smem[];
   unsigned char* s_o = smem + 2 * SM::IN_BYTES;

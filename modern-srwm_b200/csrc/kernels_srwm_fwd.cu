@@ -1,4 +1,4 @@
-// Instantiations of srwm_fwd_kernel for every compiled configuration (configs.h).
+// Instantiations of the SRWM forward kernels for every compiled configuration (configs.h).
 // Built twice: -DSRWM_TIO_BF16=0 (fp32 streams) and -DSRWM_TIO_BF16=1 (bf16 streams).
 #include "configs.h"
 #include "launch.h"
@@ -12,16 +12,16 @@ typedef __nv_bfloat16 TIO;
 typedef float TIO;
 #endif
 
-// The extended form of a call (flag bits above the ABI's three) runs the EXT instantiation
-// of the default configuration; the plain form keeps its own, unchanged code.
+// The layer-level form of a call (flag bits above the ABI's three) runs the LAYER instantiation
+// of a configuration; the plain form keeps its own code.
 constexpr unsigned EXT_FLAGS = F_INPUT_SOFTMAX | F_BASE | F_SHIFT_IN | F_DONE;
 
-template <int E, int V, int P, int R, int T, bool PK, int MINB>
+template <int E, int V, int P, int R, int T, bool PK, int MINB, int LAYER>
 int run(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
   if (p.flags & EXT_FLAGS) {
-    if constexpr (V == 0) {
+    if constexpr (LAYER) {
       constexpr int smem = SrwmFwdSmem<TIO, E, T, true>::TOTAL;
-      if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; }
+      if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; info->id = V; }
       if (describe_only) return 0;
       static unsigned long long dev_mask_ext = 0;
       return launch_kernel(srwm_fwd_kernel<TIO, E, P, R, T, PK, MINB, true>, p, grid, P, smem, s, &dev_mask_ext,
@@ -31,18 +31,18 @@ int run(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int 
     }
   }
   constexpr int smem = SrwmFwdSmem<TIO, E, T>::TOTAL;
-  if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; }
+  if (info) { info->P = P; info->R = R; info->T = T; info->smem = smem; info->id = V; }
   if (describe_only) return 0;
   static unsigned long long dev_mask = 0;
   return launch_kernel(srwm_fwd_kernel<TIO, E, P, R, T, PK, MINB>, p, grid, P, smem, s, &dev_mask, cuda_err);
 }
 
-template <int E, int V, int T, bool PK, int MINB, bool DPRE, int NRP>
+template <int E, int V, int T, bool PK, int MINB, bool DPRE, int NRP, int LAYER>
 int run_col(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
   if (p.flags & EXT_FLAGS) {
-    if constexpr (V == 0) {
+    if constexpr (LAYER) {
       constexpr int smem = SrwmFwdColSmem<TIO, E, T, true>::TOTAL;
-      if (info) { info->P = 96; info->R = E / NRP; info->T = T; info->smem = smem; }
+      if (info) { info->P = 96; info->R = E / NRP; info->T = T; info->smem = smem; info->id = V; }
       if (describe_only) return 0;
       static unsigned long long dev_mask_ext = 0;
       return launch_kernel(srwm_fwd_col_kernel<TIO, E, T, PK, MINB, DPRE, NRP, true>, p, grid, 96, smem, s,
@@ -52,7 +52,7 @@ int run_col(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, 
     }
   }
   constexpr int smem = SrwmFwdColSmem<TIO, E, T>::TOTAL;
-  if (info) { info->P = 96; info->R = E / NRP; info->T = T; info->smem = smem; }
+  if (info) { info->P = 96; info->R = E / NRP; info->T = T; info->smem = smem; info->id = V; }
   if (describe_only) return 0;
   static unsigned long long dev_mask = 0;
   return launch_kernel(srwm_fwd_col_kernel<TIO, E, T, PK, MINB, DPRE, NRP>, p, grid, 96, smem, s, &dev_mask, cuda_err);
@@ -66,13 +66,16 @@ int dispatch_srwm_fwd_bf16(
 int dispatch_srwm_fwd_f32(
 #endif
     int E, int variant, const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only,
-    int* cuda_err) {
-#define X(E_, V_, P_, R_, T_, PK_, MINB_) \
-  if (E == E_ && variant == V_) return run<E_, V_, P_, R_, T_, PK_, MINB_>(p, grid, s, info, describe_only, cuda_err);
+    int* cuda_err, int sms) {
+  (void)sms;
+  if (variant == 0) variant = 1;   // one configuration per head size serves every grid
+#define X(E_, V_, P_, R_, T_, PK_, MINB_, LAYER_) \
+  if (E == E_ && variant == V_) return run<E_, V_, P_, R_, T_, PK_, MINB_, LAYER_>(p, grid, s, info, describe_only, cuda_err);
   SRWM_FWD_CONFIGS(X)
 #undef X
-#define Y(E_, V_, T_, PK_, MINB_, DPRE_, NRP_) \
-  if (E == E_ && variant == V_) return run_col<E_, V_, T_, PK_, MINB_, DPRE_, NRP_>(p, grid, s, info, describe_only, cuda_err);
+#define Y(E_, V_, T_, PK_, MINB_, DPRE_, NRP_, LAYER_) \
+  if (E == E_ && variant == V_)                         \
+    return run_col<E_, V_, T_, PK_, MINB_, DPRE_, NRP_, LAYER_>(p, grid, s, info, describe_only, cuda_err);
   SRWM_FWD_COL_CONFIGS(Y)
 #undef Y
   return (E == 8 || E == 16 || E == 32 || E == 64) ? -6 : -3;

@@ -120,6 +120,8 @@ SYMBOLS = {
     "srwm_b200_last_cuda_error": (C.c_int, []),
     "srwm_b200_describe": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32,
                                      C.POINTER(C.c_int32 * 4)]),
+    "srwm_b200_describe_for_grid": (C.c_int, [C.c_int32, C.c_int32, C.c_int32, C.c_int32, C.c_int64, C.c_int32,
+                                              C.POINTER(C.c_int32 * 5)]),
 }
 
 _lib = None
@@ -162,7 +164,12 @@ def check(code, what):
         raise SrwmError(code, what)
 
 
-def describe(op, E, io_dtype=F32, variant=0):
-    out = (C.c_int32 * 4)()
-    check(load().srwm_b200_describe(op, E, io_dtype, variant, C.byref(out)), "describe")
-    return dict(P=out[0], R=out[1], T=out[2], smem=out[3])
+def describe(op, E, io_dtype=F32, variant=0, grid=None, num_sms=0):
+    """Kernel configuration of a call; with ``grid`` (= N*H sequences) what variant 0 resolves to there."""
+    if grid is None:
+        out = (C.c_int32 * 4)()
+        check(load().srwm_b200_describe(op, E, io_dtype, variant, C.byref(out)), "describe")
+        return dict(P=out[0], R=out[1], T=out[2], smem=out[3])
+    out = (C.c_int32 * 5)()
+    check(load().srwm_b200_describe_for_grid(op, E, io_dtype, variant, grid, num_sms, C.byref(out)), "describe")
+    return dict(P=out[0], R=out[1], T=out[2], smem=out[3], id=out[4])
