@@ -335,6 +335,18 @@ int         srwm_b200_describe(int32_t op, int32_t E, int32_t io_dtype, int32_t 
 int         srwm_b200_describe_for_grid(int32_t op, int32_t E, int32_t io_dtype, int32_t variant,
                                         int64_t grid, int32_t num_sms, int32_t out[5]);
 
+/* ---- debug build (csrc/build.py --debug -> libsrwm_b200_debug.so; no reference counterpart) ----
+ * In the debug build every chunk of rows a kernel stages or writes is checked against the sequence
+ * length before an address is formed; the first violation is recorded in a per-device status word and
+ * the access is skipped (nothing traps, the context stays usable).
+ * srwm_b200_debug_status: waits for the device, returns the word through *status and clears it.
+ *   0 = no violation; otherwise bit 63 | site id (8 bits) << 48 | CTA index (24) << 24 | first row (24).
+ *   Return value 0 in the debug build, 1 ("checks not compiled in", *status = 0) in the ordinary one.
+ * srwm_b200_debug_selftest: launches a one-warp kernel that runs the check on a chunk starting before
+ *   the sequence (site id 255) without touching memory, so that the reporting path can be tested. */
+int         srwm_b200_debug_status(uint64_t* status);
+int         srwm_b200_debug_selftest(void* cuda_stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -6,9 +6,28 @@
 #include "configs.h"
 #include "launch.h"
 
+#ifdef SRWM_DEBUG_CHECKS
+// Status word of the debug build's row checks (common.cuh::bad_rows), one per device.
+__device__ unsigned long long g_debug_status = 0ull;
+#endif
+
 namespace {
 
 thread_local int g_last_cuda_error = 0;
+
+// Device address of the status word (debug build), null in the ordinary build.
+inline unsigned long long* debug_word() {
+#ifdef SRWM_DEBUG_CHECKS
+  unsigned long long* ptr = nullptr;
+  if (cudaGetSymbolAddress((void**)&ptr, g_debug_status) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  return ptr;
+#else
+  return nullptr;
+#endif
+}
 
 inline int esize(int dtype) { return dtype == SRWM_B200_BF16 ? 2 : 4; }
 
@@ -205,6 +224,7 @@ int srwm_b200_srwm_layer_forward(const srwm_b200_srwm_fwd_args* a, const srwm_b2
   if (int rc = check_ext(x, /*forward=*/true, &ext_flags)) return rc;
 
   srwm::SrwmFwdParams p = {};
+  p.dbg = debug_word();
   p.N = a->N; p.H = a->H; p.L = a->L;
   p.flags = (a->flags & (SRWM_B200_FLAG_NO_SAVE | SRWM_B200_FLAG_INPUT_SOFTMAX)) | ext_flags;
   if (ext_flags & srwm::F_BASE) {
@@ -249,6 +269,7 @@ int srwm_b200_srwm_layer_backward(const srwm_b200_srwm_bwd_args* a, const srwm_b
   if (int rc = check_ext(x, /*forward=*/false, &ext_flags)) return rc;
 
   srwm::SrwmBwdParams p = {};
+  p.dbg = debug_word();
   p.N = a->N; p.H = a->H; p.L = a->L;
   p.flags = (a->flags & (SRWM_B200_FLAG_STATE_GRAD_IN | SRWM_B200_FLAG_RESTORE_STATE | SRWM_B200_FLAG_INPUT_SOFTMAX)) |
             ext_flags;
@@ -286,6 +307,7 @@ int srwm_b200_srwm_backward_detached(const srwm_b200_srwm_bwd_detached_args* a, 
   if (!ok) return SRWM_B200_ERR_ALIGN;
 
   srwm::SrwmBwdDetParams p = {};
+  p.dbg = debug_word();
   p.N = a->N; p.H = a->H; p.L = a->L;
   p.flags = (a->flags & SRWM_B200_FLAG_INPUT_SOFTMAX) | (a->shift_W_y.data ? srwm::F_SHIFT_IN : 0u) |
             (a->done ? srwm::F_DONE : 0u);
@@ -317,6 +339,7 @@ int srwm_b200_delta_forward(const srwm_b200_delta_fwd_args* a, void* stream) {
   if (!ok) return SRWM_B200_ERR_ALIGN;
 
   srwm::DeltaFwdParams p = {};
+  p.dbg = debug_word();
   p.N = a->N; p.H = a->H; p.L = a->L; p.flags = a->flags & SRWM_B200_FLAG_NO_SAVE;
   p.Q = view(a->Q, es); p.K = view(a->K, es); p.V = view(a->V, es); p.beta = view(a->beta, es);
   p.out = view(a->out, es); p.v_old = view(a->v_old, 4); p.v_ins = view(a->v_insert, 4);
@@ -349,6 +372,7 @@ int srwm_b200_delta_backward(const srwm_b200_delta_bwd_args* a, void* stream) {
   if (!ok) return SRWM_B200_ERR_ALIGN;
 
   srwm::DeltaBwdParams p = {};
+  p.dbg = debug_word();
   p.N = a->N; p.H = a->H; p.L = a->L; p.flags = 0;
   p.Q = view(a->Q, es); p.K = view(a->K, es); p.V = view(a->V, es); p.beta = view(a->beta, es);
   p.v_old = view(a->v_old, 4); p.v_ins = view(a->v_insert, 4); p.gout = view(a->grad_out, es);
@@ -377,6 +401,7 @@ int srwm_b200_delta_packed_forward(const srwm_b200_delta_packed_fwd_args* a, voi
   if (!ok) return SRWM_B200_ERR_ALIGN;
 
   srwm::DeltaFwdParams p = {};
+  p.dbg = debug_word();
   p.N = a->N; p.H = a->H; p.L = a->L;
   p.flags = (a->flags & SRWM_B200_FLAG_NO_SAVE) | srwm::F_PACKED |
             ((a->flags & SRWM_B200_FLAG_ZERO_INIT) ? srwm::F_ZERO_INIT : 0u);
@@ -409,6 +434,7 @@ int srwm_b200_delta_packed_backward(const srwm_b200_delta_packed_bwd_args* a, vo
   if (!ok) return SRWM_B200_ERR_ALIGN;
 
   srwm::DeltaBwdParams p = {};
+  p.dbg = debug_word();
   p.N = a->N; p.H = a->H; p.L = a->L;
   p.flags = srwm::F_PACKED;
   p.eps = a->norm_eps;
@@ -420,6 +446,50 @@ int srwm_b200_delta_packed_backward(const srwm_b200_delta_packed_bwd_args* a, vo
                      ? srwm::dispatch_delta_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0)
                      : srwm::dispatch_delta_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0);
   return finish(rc, ce);
+}
+
+#ifdef SRWM_DEBUG_CHECKS
+namespace {
+__global__ void debug_selftest_kernel(unsigned long long* dbg) {
+  // a chunk that starts before the sequence: must be recorded and reported as bad, touching nothing
+  (void)SRWM_BAD_ROWS(dbg, 255, -16, 16, 0, 16);
+}
+}  // namespace
+#endif
+
+int srwm_b200_debug_status(uint64_t* status) {
+  if (!status) return SRWM_B200_ERR_NULL;
+  *status = 0;
+#ifdef SRWM_DEBUG_CHECKS
+  unsigned long long w = 0ull, zero = 0ull;
+  cudaError_t e = cudaMemcpyFromSymbol(&w, g_debug_status, sizeof(w));   // waits for the kernels in flight
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(g_debug_status, &zero, sizeof(zero));
+  if (e != cudaSuccess) {
+    g_last_cuda_error = (int)e;
+    return SRWM_B200_ERR_CUDA;
+  }
+  *status = w;
+  return 0;
+#else
+  return 1;
+#endif
+}
+
+int srwm_b200_debug_selftest(void* stream) {
+#ifdef SRWM_DEBUG_CHECKS
+  unsigned long long* w = debug_word();
+  if (!w) return SRWM_B200_ERR_CUDA;
+  debug_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(w);
+  const cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    g_last_cuda_error = (int)e;
+    return SRWM_B200_ERR_CUDA;
+  }
+  return 0;
+#else
+  (void)stream;
+  return 1;
+#endif
 }
 
 }  // extern "C"

@@ -57,7 +57,14 @@ def _compile(job):
     return obj, r.returncode, r.stdout + r.stderr
 
 
-def build(force=False, verbose=False, tuning=None):
+def build(force=False, verbose=False, tuning=None, debug=False):
+    if debug:   # a separate library with the row checks compiled in (objects in their own directory)
+        return _build(os.path.join(CSRC, "build_debug"), os.path.join(PKG, "srwm_b200", "libsrwm_b200_debug.so"),
+                      force, verbose, False, ["-DSRWM_DEBUG_CHECKS"])
+    return _build(OBJ, LIB, force, verbose, tuning, [])
+
+
+def _build(OBJ, LIB, force, verbose, tuning, extra_flags):
     os.makedirs(OBJ, exist_ok=True)
     hdrs = _headers()
     # the flag set the objects were built with; a change rebuilds everything.  tuning=None keeps
@@ -69,7 +76,7 @@ def build(force=False, verbose=False, tuning=None):
     cur = "tuning" if tuning else "product"
     if cur != prev:
         force = True
-    extra_all = ["-DSRWM_TUNING_VARIANTS"] if tuning else []
+    extra_all = (["-DSRWM_TUNING_VARIANTS"] if tuning else []) + list(extra_flags)
     jobs = []
     for tu in KERNEL_TUS:
         src = os.path.join(CSRC, tu + ".cu")
@@ -114,5 +121,8 @@ if __name__ == "__main__":
     ap.add_argument("--verbose", action="store_true", help="print ptxas register / spill report")
     ap.add_argument("--tuning", action="store_true", help="also compile the tuning alternatives of configs.h")
     ap.add_argument("--product", action="store_true", help="compile only the configurations the library picks")
+    ap.add_argument("--debug", action="store_true",
+                    help="build libsrwm_b200_debug.so: row checks that report through a status word")
     a = ap.parse_args()
-    print(build(force=a.force, verbose=a.verbose, tuning=True if a.tuning else (False if a.product else None)))
+    print(build(force=a.force, verbose=a.verbose, tuning=True if a.tuning else (False if a.product else None),
+                debug=a.debug))

@@ -326,6 +326,27 @@ __device__ __forceinline__ void flush_rows(void* gdst_row0, long long row_stride
 // far inside the 1e-4 forward tolerance, and the backward consumes the SAVED results).
 __device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
+// Debug build (-DSRWM_DEBUG_CHECKS): every staged / flushed chunk of rows is checked against the
+// sequence length before any address is formed.  A violation is recorded once in a status word
+// (bit 63 set | site id << 48 | CTA index (24 bits) << 24 | first row (24 bits)) and the access is
+// skipped; nothing traps.  The C ABI returns the word (srwm_b200_debug_status).  In the ordinary
+// build the check compiles to nothing.
+#ifdef SRWM_DEBUG_CHECKS
+__device__ __forceinline__ bool bad_rows(unsigned long long* dbg, int site, int t0, int nt, int L, int T) {
+  if (t0 >= 0 && nt >= 0 && nt <= T && t0 + nt <= L) return false;
+  if (dbg != nullptr && threadIdx.x == 0) {
+    const unsigned long long w = (1ull << 63) | ((unsigned long long)(site & 0xff) << 48) |
+                                 ((unsigned long long)(blockIdx.x & 0xffffffu) << 24) |
+                                 (unsigned long long)((unsigned)t0 & 0xffffffu);
+    atomicCAS(dbg, 0ull, w);
+  }
+  return true;
+}
+#define SRWM_BAD_ROWS(dbg, site, t0, nt, L, T) ::srwm::bad_rows(dbg, site, t0, nt, L, T)
+#else
+#define SRWM_BAD_ROWS(dbg, site, t0, nt, L, T) false
+#endif
+
 // A sequence view with byte strides, as passed to the kernels.
 struct SeqView {
   char* base;

@@ -27,6 +27,7 @@ constexpr unsigned F_PACKED = 8u, F_ZERO_INIT = 16u;
 struct DeltaFwdParams {
   int N, H, L;
   unsigned flags;
+  unsigned long long* dbg;   // status word of the debug build (null otherwise)
   int seq0;   // first sequence of this launch (a call may be split into launches of different configurations)
   SeqView Q, K, V, beta, out, v_old, v_ins;   // Q doubles as the packed rows
   StateView W;
@@ -36,6 +37,7 @@ struct DeltaFwdParams {
 struct DeltaBwdParams {
   int N, H, L;
   unsigned flags;
+  unsigned long long* dbg;   // status word of the debug build (null otherwise)
   int seq0;   // first sequence of this launch
   SeqView Q, K, V, beta, v_old, v_ins, gout, gQ, gK, gV, gbeta;   // Q / gQ double as the packed rows
   StateView W, gW0;
@@ -159,6 +161,7 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
   auto in_buf = [&](int b) { return smem + b * SM::IN_BYTES; };
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 5, t0, nt, L, T)) return;
     unsigned char* ib = in_buf(c & 1);
     if constexpr (PACKED) {
       stage_packed_rows<SM::RSB, SM::PK_PITCH, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, tid);
@@ -180,6 +183,7 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_kernel(const DeltaFwdParams
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 5, t0, nt, L, T)) break;
     const bool has_next = (c + 1 < nchunks);
     const int nt_next = has_next ? min(T, L - (t0 + T)) : 0;
     float bnext[(T + P - 1) / P];
@@ -364,6 +368,7 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdPa
   auto in_buf = [&](int b) { return smem + b * SM::IN_BYTES; };
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 6, t0, nt, L, T)) return;
     unsigned char* ib = in_buf(c & 1);
     if constexpr (PACKED) {
       stage_packed_rows<SM::RSB, SM::PK_PITCH, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, lane);
@@ -383,6 +388,7 @@ __global__ void __launch_bounds__(P, MINB) delta_fwd_col_kernel(const DeltaFwdPa
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 6, t0, nt, L, T)) break;
     const bool has_next = (c + 1 < nchunks);
     const int nt_next = has_next ? min(T, L - (t0 + T)) : 0;
     float bnext = 0.f;
@@ -575,6 +581,7 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
   auto in_buf = [&](int b) { return smem + b * SM::IN_BYTES; };
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 7, t0, nt, L, T)) return;
     unsigned char* ib = in_buf(c & 1);
     if constexpr (PACKED) {
       stage_packed_rows<SM::RSB, SM::PK_PITCH, P>(ib, p.Q.row(n, h, t0), p.Q.sl, nt, tid);
@@ -606,6 +613,7 @@ __global__ void __launch_bounds__(P, MINB) delta_bwd_kernel(const DeltaBwdParams
 
   for (int c = nchunks - 1; c >= 0; --c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 7, t0, nt, L, T)) break;
     const bool has_next = (c > 0);
     float bnext[(T + P - 1) / P];
     if (has_next) {

@@ -36,6 +36,7 @@ namespace srwm {
 struct SrwmFwdParams {
   int N, H, L;
   unsigned flags;
+  unsigned long long* dbg;   // status word of the debug build (null otherwise)
   SeqView x, out, q, k, beta, yd, qd, kd, bd;
   StateView Wy, Wq, Wk, wb;
   StateView bWy, bWq, bWk, bwb;   // slow weights
@@ -47,6 +48,7 @@ struct SrwmFwdParams {
 struct SrwmBwdParams {
   int N, H, L;
   unsigned flags;
+  unsigned long long* dbg;   // status word of the debug build (null otherwise)
   SeqView x, q, k, beta, yd, qd, kd, bd, gout, gx;
   StateView Wy, Wq, Wk, wb, gWy, gWq, gWk, gwb;
   StateView bWy, bWq, bWk, bwb;   // slow weights
@@ -186,6 +188,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
   auto in_buf = [&](int b) { return reinterpret_cast<TIO*>(smem + b * SM::IN_BYTES); };
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 1, t0, nt, L, T)) return;
     stage_rows<SM::ROW_IO, P>(in_buf(c & 1), p.x.row(n, h, t0), p.x.sl, nt, tid);
   };
   stage_chunk(0);
@@ -197,6 +200,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_fwd_kernel(const SrwmFwdParams p
   int par = 0;
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 1, t0, nt, L, T)) break;
     if (c + 1 < nchunks) stage_chunk(c + 1);
     cp_async_commit();
     if (has_done) {
@@ -508,6 +512,7 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
   auto in_buf = [&](int b) { return reinterpret_cast<TIO*>(smem + b * SM::IN_BYTES); };
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 2, t0, nt, L, T)) return;
     stage_rows<SM::ROW_IO, P>(in_buf(c & 1), p.x.row(n, h, t0), p.x.sl, nt, tid);
   };
   stage_chunk(0);
@@ -520,6 +525,7 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 2, t0, nt, L, T)) break;
     if (c + 1 < nchunks) stage_chunk(c + 1);
     cp_async_commit();
     if (has_done) {
@@ -847,6 +853,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
   auto in_buf = [&](int b) { return smem + b * SM::IN_BYTES; };
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 3, t0, nt, L, T)) return;
     unsigned char* ib = in_buf(c & 1);
     stage_rows<SM::ROW_IO, P>(ib, p.x.row(n, h, t0), p.x.sl, nt, tid);
     stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.gout.row(n, h, t0), p.gout.sl, nt, tid);
@@ -866,6 +873,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
   int par = 0;
   for (int c = nchunks - 1; c >= 0; --c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 3, t0, nt, L, T)) break;
     if (c > 0) stage_chunk(c - 1);
     cp_async_commit();
     cp_async_wait<1>();
@@ -1300,6 +1308,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
 struct SrwmBwdDetParams {
   int N, H, L;
   unsigned flags;                 // F_INPUT_SOFTMAX, F_SHIFT_IN, F_DONE
+  unsigned long long* dbg;   // status word of the debug build (null otherwise)
   SeqView x, k, beta, yd, gout, gx;
   StateView bWy, sWy, gWy;        // initial W_y = bWy (+ sWy); gWy receives sum_t x_t^T g_t
   const unsigned char* done;
@@ -1348,6 +1357,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_det_kernel(const SrwmBwdDetP
   auto in_buf = [&](int b) { return smem + b * SM::IN_BYTES; };
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 4, t0, nt, L, T)) return;
     unsigned char* ib = in_buf(c & 1);
     stage_rows<SM::ROW_IO, P>(ib, p.x.row(n, h, t0), p.x.sl, nt, tid);
     stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.gout.row(n, h, t0), p.gout.sl, nt, tid);
@@ -1363,6 +1373,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_det_kernel(const SrwmBwdDetP
 
   for (int c = 0; c < nchunks; ++c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 4, t0, nt, L, T)) break;
     if (c + 1 < nchunks) stage_chunk(c + 1);
     cp_async_commit();
     if (has_done) {

@@ -135,6 +135,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd2_kernel(const SrwmBwdParams 
   auto in_buf = [&](int b) { return smem + b * SM::IN_BYTES; };
   auto stage_chunk = [&](int c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 8, t0, nt, L, T)) return;
     unsigned char* ib = in_buf(c & 1);
     stage_rows<SM::ROW_IO, P>(ib, p.x.row(n, h, t0), p.x.sl, nt, tid);
     stage_rows<SM::ROW_IO, P>(ib + T * SM::ROW_IO, p.gout.row(n, h, t0), p.gout.sl, nt, tid);
@@ -155,6 +156,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd2_kernel(const SrwmBwdParams 
   int par = 0;
   for (int c = nchunks - 1; c >= 0; --c) {
     const int t0 = c * T, nt = min(T, L - t0);
+    if (SRWM_BAD_ROWS(p.dbg, 8, t0, nt, L, T)) break;
     if (c > 0) stage_chunk(c - 1);
     cp_async_commit();
     cp_async_wait<1>();

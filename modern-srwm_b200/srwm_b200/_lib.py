@@ -10,7 +10,10 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libsrwm_b200.so")
+# SRWM_B200_DEBUG=1 selects the debug build of the library (row checks that report through a status
+# word instead of faulting; csrc/build.py --debug)
+DEBUG_BUILD = os.environ.get("SRWM_B200_DEBUG", "0") not in ("", "0")
+LIB_PATH = os.path.join(_HERE, "libsrwm_b200_debug.so" if DEBUG_BUILD else "libsrwm_b200.so")
 
 F32, BF16 = 0, 1
 FLAG_NO_SAVE, FLAG_STATE_GRAD_IN, FLAG_RESTORE_STATE, FLAG_INPUT_SOFTMAX, FLAG_ZERO_INIT = 1, 2, 4, 8, 16
@@ -113,6 +116,8 @@ SYMBOLS = {
     "srwm_b200_delta_packed_backward": (C.c_int, [C.POINTER(DeltaPackedBwdArgs), C.c_void_p]),
     "srwm_b200_reduce_batch": (C.c_int, [C.c_void_p, C.c_int64, C.c_int32, C.c_int64, C.c_void_p,
                                          C.c_int32, C.c_void_p]),
+    "srwm_b200_debug_status": (C.c_int, [C.POINTER(C.c_uint64)]),
+    "srwm_b200_debug_selftest": (C.c_int, [C.c_void_p]),
     "srwm_b200_abi_version": (C.c_int, []),
     "srwm_b200_head_dim_supported": (C.c_int, [C.c_int32]),
     "srwm_b200_num_variants": (C.c_int, [C.c_int32, C.c_int32]),
@@ -135,7 +140,8 @@ def load():
     if not os.path.exists(LIB_PATH):
         raise RuntimeError(
             f"{LIB_PATH} is missing: build it with "
-            "`python modern-srwm_b200/csrc/build.py` (there is no fallback implementation)")
+            "`python modern-srwm_b200/csrc/build.py" + (" --debug" if DEBUG_BUILD else "") +
+            "` (there is no fallback implementation)")
     lib = C.CDLL(LIB_PATH)
     for name, (res, args) in SYMBOLS.items():
         fn = getattr(lib, name, None)
@@ -173,3 +179,13 @@ def describe(op, E, io_dtype=F32, variant=0, grid=None, num_sms=0):
     out = (C.c_int32 * 5)()
     check(load().srwm_b200_describe_for_grid(op, E, io_dtype, variant, grid, num_sms, C.byref(out)), "describe")
     return dict(P=out[0], R=out[1], T=out[2], smem=out[3], id=out[4])
+
+
+def debug_status():
+    """(compiled_in, word): the debug build's status word (0 = no violation), cleared by the read."""
+    w = C.c_uint64(0)
+    rc = load().srwm_b200_debug_status(C.byref(w))
+    if rc == 1:
+        return False, 0
+    check(rc, "debug_status")
+    return True, int(w.value)

@@ -262,3 +262,15 @@ def rel_max(a, b):
     a = a.double()
     b = b.double()
     return float((a - b).abs().max() / (b.abs().max() + 1e-300))
+
+
+def rel_elem(a, b, floor=1e-3):
+    """Element-wise relative error max |a-b| / |b| over the elements with |b| > floor * max|b|:
+    the reference's metric (self_ref_v0/__init__.py:232-233) with its absolute 1e-6 guard replaced
+    by a floor relative to the tensor's scale, so that it means the same for tensors of any scale."""
+    a = a.double()
+    b = b.double()
+    m = b.abs() > floor * b.abs().max()
+    if not bool(m.any()):
+        return 0.0
+    return float(((a - b).abs()[m] / b.abs()[m]).max())
