@@ -6,9 +6,9 @@
         --master-port P bench.py --gpus N --steps K --warmup W
 
 A "step" is one forward + backward pass of the operator over the (rank-local shard of the)
-workload's batch, followed by the reduction of the per-sample state gradients into the
-slow-weight gradient bucket and, for N > 1, its NCCL all-reduce (enqueued behind the
-reduction and overlapped with the next step's forward).  The default workload is the
+workload's batch -- the backward also sums the per-sample state gradients over the local batch
+into the slow-weight gradient bucket -- and, for N > 1, the bucket's NCCL all-reduce (enqueued
+behind the backward and overlapped with the next step's forward).  The default workload is the
 scale-sweep configuration: SRWM, B=1024 (global, batch-sharded over the ranks), H=16,
 d_head=64, L=2048, bf16 activations, fp32 state, run through the layer-level entry points with
 the slow weights un-repeated ([1,H,d,.], batch stride 0).  The same run also times the
@@ -310,8 +310,9 @@ def config_of(name, wl, n):
     return {"workload": f"{name}: {wl['op']} fwd+bwd B={wl['B']} H={wl['H']} L={wl['L']} d_head={wl['E']} "
                         f"{wl['dtype']} activations, fp32 state",
             "global_batch": wl["B"], "seq_len": wl["L"], "heads": wl["H"], "d_head": wl["E"],
-            "parallelism": f"batch-sharded x{n}" + ("; slow weights un-repeated [1,H,d,.], per-sample gradients "
-                                                     "batch-reduced into one flat bucket, one NCCL all-reduce per step"
+            "parallelism": f"batch-sharded x{n}" + ("; slow weights un-repeated [1,H,d,.], batch reduction of the "
+                                                     "gradients fused into the backward (into one flat bucket), "
+                                                     "one NCCL all-reduce per step"
                                                      if wl["op"].startswith("srwm") else ""),
             "l2": "inputs_exceed_l2"}
 
@@ -384,16 +385,16 @@ class OpBench:
             if rec: rec[0].record()
             out, shift_out, saved = lo.srwm_layer_forward(self.x, self.slow, None, None, input_softmax=False)
             if rec: rec[1].record()
-            grads = lo.srwm_layer_backward(self.x, saved, self.go, self.slow, shift_out, None, input_softmax=False)
-            if rec: rec[2].record()
-            # batch sum of the per-sample dL/dW_0 straight into the flat bucket, then its all-reduce
-            # behind it (asynchronous: it overlaps the next step's forward)
+            # the backward sums the per-sample dL/dW_0 over the local batch straight into the flat bucket
+            # (fused into the kernel's epilogue); the bucket's all-reduce is enqueued behind it and
+            # overlaps the next step's forward, so the previous one must have landed before this backward
             self.bucket.wait()
-            for i in range(4):
-                self.bucket.reduce_into(i, grads[1 + i])
+            grads = lo.srwm_layer_backward(self.x, saved, self.go, self.slow, shift_out, None, input_softmax=False,
+                                           reduce_into=[self.bucket.view(i) for i in range(4)])
+            if rec: rec[2].record()
             self.bucket.all_reduce(async_op=True)
             self.last = (out, grads[0])
-            self.launches_per_step = 2 + 4
+            self.launches_per_step = 2
         elif op == "srwm_layer":
             if rec: rec[0].record()
             out, shift_out, saved = lo.srwm_layer_forward(self.x, self.slow, self.shift, self.done, True)

@@ -7,7 +7,8 @@
  * C: device pointers, sizes, element strides, a CUDA stream handle passed as void*.
  * No buffer is owned by the library and no state is kept between calls (the calls are
  * re-entrant; concurrent calls from several host threads are fine as long as each uses
- * its own buffers).  Nothing is allocated on the device by these calls.
+ * its own buffers).  Nothing is allocated on the device by these calls; the one call that
+ * needs working memory beyond its inputs and outputs takes it from the caller.
  *
  * Conventions
  *   - Sequence tensors are 4-D views [N, H, L, X] (batch, head, time, feature) whose
@@ -31,6 +32,7 @@
 #ifndef SRWM_B200_H_
 #define SRWM_B200_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -52,7 +54,9 @@ extern "C" {
 #define SRWM_B200_ERR_ALIGN      -5  /* a row does not start on a 16-byte boundary        */
 #define SRWM_B200_ERR_VARIANT    -6  /* tuning variant id not compiled in                 */
 #define SRWM_B200_ERR_CUDA       -7  /* CUDA runtime error; see srwm_b200_last_cuda_error */
-#define SRWM_B200_ERR_TOO_LARGE  -8  /* size beyond a fixed capacity (reserved)           */
+#define SRWM_B200_ERR_TOO_LARGE  -8  /* size beyond a fixed capacity / scratch too small     */
+#define SRWM_B200_ERR_UNSUPPORTED -9 /* combination of arguments the entry point cannot serve
+                                        (e.g. `done` given to the reverse-time layer backward) */
 
 /* flags */
 #define SRWM_B200_FLAG_NO_SAVE        1u /* forward: do not write the saved-for-backward
@@ -158,7 +162,10 @@ int srwm_b200_srwm_backward(const srwm_b200_srwm_bwd_args* args, void* cuda_stre
  *              zero before step t -- the per-step `nd * state` of the learner's unroll
  *              (reinforcement_learning/torchbeast_procgen/model.py:1180-1194), which lets T
  *              one-step calls become one call of length T.  The reverse-time backward cannot
- *              cross such a reset (the pre-reset state is gone); use the detached backward.
+ *              cross such a reset (the pre-reset state is gone): srwm_b200_srwm_layer_backward
+ *              returns SRWM_B200_ERR_UNSUPPORTED when `done` is set; use the detached backward.
+ * With L == 0 the forward is a no-op that leaves W_* untouched (the caller carries the shift
+ * through: shift_in, or zero).
  * ext == NULL (or all base_* NULL) makes these identical to the plain calls above.
  * ---------------------------------------------------------------------------------- */
 typedef struct srwm_b200_srwm_ext {
@@ -173,6 +180,32 @@ int srwm_b200_srwm_layer_forward(const srwm_b200_srwm_fwd_args* args, const srwm
                                  void* cuda_stream);
 int srwm_b200_srwm_layer_backward(const srwm_b200_srwm_bwd_args* args, const srwm_b200_srwm_ext* ext,
                                   void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------
+ * Layer-level SRWM backward with the batch reduction fused into it.  The gradient of the
+ * un-repeated slow weights is the sum over the batch of the per-sample dL/dW_0 -- the backward of
+ * the callers' `W.repeat(bsz, 1, 1, 1)` (supervised_learning/layer.py:174-177, no reference
+ * function corresponds one to one).  grad_W_* of the main block still receive the per-sample
+ * gradients (dL/dshift); in addition grad_base_* receive their batch sums, formed inside the
+ * backward kernel: the CTAs of one head are grouped by consecutive samples, the CTA of a group
+ * that finishes last adds the group's gradients in sample order, the group of a head that
+ * finishes last adds the group sums in group order (atomic counters tell which; no CTA waits for
+ * another).  Every addition has a fixed order: the result is deterministic.
+ * `scratch` is device memory of srwm_b200_srwm_reduce_scratch_bytes(N, H, E) bytes, 256-byte
+ * aligned, used only during the call (calls that overlap on the GPU need separate scratch).
+ * ---------------------------------------------------------------------------------- */
+typedef struct srwm_b200_srwm_reduce {
+  srwm_b200_state grad_base_W_y, grad_base_W_q, grad_base_W_k;   /* out [1,H,E,E] fp32 (stride_n unused) */
+  srwm_b200_state grad_base_w_b;                                 /* out [1,H,E,4] */
+  int32_t accumulate;               /* != 0: add to what grad_base_* hold instead of overwriting */
+  int32_t reserved;
+  void*   scratch;
+  int64_t scratch_bytes;
+} srwm_b200_srwm_reduce;
+
+size_t srwm_b200_srwm_reduce_scratch_bytes(int32_t N, int32_t H, int32_t E);   /* 0 for invalid sizes */
+int srwm_b200_srwm_layer_backward_reduced(const srwm_b200_srwm_bwd_args* args, const srwm_b200_srwm_ext* ext,
+                                          const srwm_b200_srwm_reduce* red, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------
  * SRWM backward with the state DETACHED at every step: the gradient the reference's

@@ -88,6 +88,8 @@ inline int check_ext(const srwm_b200_srwm_ext* x, bool forward, unsigned* flags)
     *flags |= srwm::F_SHIFT_IN;
   }
   if (forward && x->done) *flags |= srwm::F_DONE;
+  // a reverse-time backward cannot cross an in-kernel reset (the pre-reset state is gone)
+  if (!forward && x->done) return SRWM_B200_ERR_UNSUPPORTED;
   return 0;
 }
 
@@ -122,6 +124,7 @@ const char* srwm_b200_strerror(int code) {
     case SRWM_B200_ERR_VARIANT: return "kernel variant not compiled in";
     case SRWM_B200_ERR_CUDA: return "CUDA runtime error (see srwm_b200_last_cuda_error)";
     case SRWM_B200_ERR_TOO_LARGE: return "size exceeds the fixed capacity of this entry point";
+    case SRWM_B200_ERR_UNSUPPORTED: return "this combination of arguments is not supported by the entry point";
     default: return "unknown error code";
   }
 }
@@ -243,7 +246,47 @@ int srwm_b200_srwm_layer_forward(const srwm_b200_srwm_fwd_args* a, const srwm_b2
   return finish(rc, ce);
 }
 
+namespace {
+// group size of the fused batch reduction, and the scratch it needs: [H][ng+1] counters (padded to 256
+// bytes), then [H][ng] partial states when there is more than one group
+constexpr int REDUCE_GROUP = 32;
+inline int reduce_groups(int N) { return N <= 2 * REDUCE_GROUP ? 1 : (N + REDUCE_GROUP - 1) / REDUCE_GROUP; }
+inline int reduce_group_size(int N) { return N <= 2 * REDUCE_GROUP ? (N > 0 ? N : 1) : REDUCE_GROUP; }
+inline size_t reduce_counter_bytes(int N, int H) {
+  return (((size_t)H * (reduce_groups(N) + 1) * 4) + 255) / 256 * 256;
+}
+inline size_t reduce_scratch_bytes(int N, int H, int E) {
+  const int ng = reduce_groups(N);
+  return reduce_counter_bytes(N, H) + (ng > 1 ? (size_t)H * ng * (3 * E * E + 4 * E) * 4 : 0);
+}
+int layer_backward_impl(const srwm_b200_srwm_bwd_args* a, const srwm_b200_srwm_ext* x,
+                        const srwm_b200_srwm_reduce* red, void* scratch, void* stream);
+}  // namespace
+
+size_t srwm_b200_srwm_reduce_scratch_bytes(int32_t N, int32_t H, int32_t E) {
+  if (N < 0 || H < 0 || !head_dim_ok(E)) return 0;
+  return reduce_scratch_bytes(N, H, E);
+}
+
 int srwm_b200_srwm_layer_backward(const srwm_b200_srwm_bwd_args* a, const srwm_b200_srwm_ext* x, void* stream) {
+  return layer_backward_impl(a, x, nullptr, nullptr, stream);
+}
+
+int srwm_b200_srwm_layer_backward_reduced(const srwm_b200_srwm_bwd_args* a, const srwm_b200_srwm_ext* x,
+                                          const srwm_b200_srwm_reduce* red, void* stream) {
+  if (!red) return SRWM_B200_ERR_NULL;
+  if (a && a->N > 0 && a->H > 0 && head_dim_ok(a->E)) {
+    if (!red->scratch) return SRWM_B200_ERR_NULL;
+    if ((uintptr_t)red->scratch % 256) return SRWM_B200_ERR_ALIGN;
+    if (red->scratch_bytes < 0 || (size_t)red->scratch_bytes < reduce_scratch_bytes(a->N, a->H, a->E))
+      return SRWM_B200_ERR_TOO_LARGE;
+  }
+  return layer_backward_impl(a, x, red, red->scratch, stream);
+}
+
+namespace {
+int layer_backward_impl(const srwm_b200_srwm_bwd_args* a, const srwm_b200_srwm_ext* x,
+                        const srwm_b200_srwm_reduce* red, void* scratch, void* stream) {
   if (!a) return SRWM_B200_ERR_NULL;
   long long grid;
   if (int rc = check_dims(a->N, a->H, a->L, &grid)) return rc;
@@ -281,12 +324,35 @@ int srwm_b200_srwm_layer_backward(const srwm_b200_srwm_bwd_args* a, const srwm_b
   p.yd = view(a->y_diff, 4); p.qd = view(a->q_diff, 4); p.kd = view(a->k_diff, 4); p.bd = view(a->beta_diff, 4);
   p.Wy = view(a->W_y); p.Wq = view(a->W_q); p.Wk = view(a->W_k); p.wb = view(a->w_b);
   p.gWy = view(a->grad_W_y); p.gWq = view(a->grad_W_q); p.gWk = view(a->grad_W_k); p.gwb = view(a->grad_w_b);
+  if (red) {
+    if (!red->grad_base_W_y.data || !red->grad_base_W_q.data || !red->grad_base_W_k.data || !red->grad_base_w_b.data)
+      return SRWM_B200_ERR_NULL;
+    if (!state_aligned(red->grad_base_W_y) || !state_aligned(red->grad_base_W_q) ||
+        !state_aligned(red->grad_base_W_k) || !state_aligned(red->grad_base_w_b))
+      return SRWM_B200_ERR_ALIGN;
+    p.flags |= srwm::F_REDUCE;
+    p.red.oWy = view(red->grad_base_W_y); p.red.oWq = view(red->grad_base_W_q);
+    p.red.oWk = view(red->grad_base_W_k); p.red.owb = view(red->grad_base_w_b);
+    p.red.gs = reduce_group_size(a->N);
+    p.red.ng = reduce_groups(a->N);
+    p.red.accumulate = red->accumulate != 0;
+    p.red.cnt = reinterpret_cast<unsigned*>(scratch);
+    p.red.part = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + reduce_counter_bytes(a->N, a->H));
+    // the counters start at zero (the kernel leaves them at zero too; clearing them here keeps a call
+    // independent of what an aborted earlier call may have left behind)
+    const cudaError_t e = cudaMemsetAsync(scratch, 0, reduce_counter_bytes(a->N, a->H), (cudaStream_t)stream);
+    if (e != cudaSuccess) {
+      g_last_cuda_error = (int)e;
+      return SRWM_B200_ERR_CUDA;
+    }
+  }
   int ce = 0;
   const int rc = a->io_dtype == SRWM_B200_BF16
                      ? srwm::dispatch_srwm_bwd_bf16(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0)
                      : srwm::dispatch_srwm_bwd_f32(a->E, a->variant, p, (int)grid, (cudaStream_t)stream, nullptr, 0, &ce, 0);
   return finish(rc, ce);
 }
+}  // namespace
 
 int srwm_b200_srwm_backward_detached(const srwm_b200_srwm_bwd_detached_args* a, void* stream) {
   if (!a) return SRWM_B200_ERR_NULL;

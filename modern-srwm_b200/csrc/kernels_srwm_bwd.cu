@@ -13,7 +13,7 @@ typedef float TIO;
 #endif
 
 // The layer-level form of a call runs the LAYER instantiation of a configuration.
-constexpr unsigned EXT_FLAGS = F_INPUT_SOFTMAX | F_BASE;
+constexpr unsigned EXT_FLAGS = F_INPUT_SOFTMAX | F_BASE | F_REDUCE;
 
 template <int E, int V, int P, int R, int T, bool PK, int MINB, int LAYER>
 int run(const SrwmBwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {

@@ -44,8 +44,13 @@ int run_col(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, 
       constexpr int smem = SrwmFwdColSmem<TIO, E, T, true>::TOTAL;
       if (info) { info->P = 96; info->R = E / NRP; info->T = T; info->smem = smem; info->id = V; }
       if (describe_only) return 0;
+      if (p.flags & F_DONE) {
+        static unsigned long long dev_mask_rst = 0;
+        return launch_kernel(srwm_fwd_col_kernel<TIO, E, T, PK, MINB, DPRE, NRP, true, true>, p, grid, 96, smem, s,
+                             &dev_mask_rst, cuda_err);
+      }
       static unsigned long long dev_mask_ext = 0;
-      return launch_kernel(srwm_fwd_col_kernel<TIO, E, T, PK, MINB, DPRE, NRP, true>, p, grid, 96, smem, s,
+      return launch_kernel(srwm_fwd_col_kernel<TIO, E, T, PK, MINB, DPRE, NRP, true, false>, p, grid, 96, smem, s,
                            &dev_mask_ext, cuda_err);
     } else {
       return -6;

@@ -45,6 +45,22 @@ struct SrwmFwdParams {
   long long done_sn, done_sl;
 };
 
+// Batch reduction fused into the backward (F_REDUCE): the slow-weight gradient is the sum over the
+// batch of the per-sample dL/dW_0 -- the backward of the callers' `W.repeat(bsz, 1, 1, 1)`
+// (supervised_learning/layer.py:174-177).  The CTAs of one head form groups of `gs` consecutive
+// samples; whichever CTA of a group finishes last (an atomic counter tells it; nobody waits) adds the
+// group's per-sample gradients in sample order into a partial, and whichever group of a head finishes
+// last adds the partials in group order into the output.  The order of every addition is fixed, so the
+// result does not depend on timing.  `cnt` ([H][ng+1] counters) must be zero on entry and is zero again
+// on exit; `part` holds [H][ng] partial states (not used when ng == 1).
+constexpr unsigned F_REDUCE = 128u;
+struct SrwmReduce {
+  StateView oWy, oWq, oWk, owb;   // [1,H,E,.] outputs
+  float* part;
+  unsigned* cnt;
+  int gs, ng, accumulate;
+};
+
 struct SrwmBwdParams {
   int N, H, L;
   unsigned flags;
@@ -52,7 +68,70 @@ struct SrwmBwdParams {
   SeqView x, q, k, beta, yd, qd, kd, bd, gout, gx;
   StateView Wy, Wq, Wk, wb, gWy, gWq, gWk, gwb;
   StateView bWy, bWq, bWk, bwb;   // slow weights
+  SrwmReduce red;
 };
+
+__device__ __forceinline__ void add4g(float4& a, const float* src) {
+  const float4 v = __ldcg(reinterpret_cast<const float4*>(src));   // written by other CTAs: read through L2
+  a.x += v.x; a.y += v.y; a.z += v.z; a.w += v.w;
+}
+
+// Epilogue of the backward kernels for F_REDUCE (all P threads of the CTA of sample n, head h call it
+// after storing their per-sample gradients).
+template <int E, int P>
+__device__ void reduce_epilogue(const SrwmBwdParams& p, int n, int h, int tid) {
+  __shared__ int s_last;
+  const SrwmReduce& r = p.red;
+  constexpr int STATE = 3 * E * E + 4 * E;
+  const int g = n / r.gs, n0 = g * r.gs;
+  const int members = min(r.gs, p.N - n0);
+  unsigned* cnt = r.cnt + (long long)h * (r.ng + 1);
+  __threadfence();   // this CTA's per-sample gradients are visible device-wide before it is counted
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(&cnt[g], 1u) == (unsigned)(members - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const bool single = r.ng == 1;
+  float* part = r.part + ((long long)h * r.ng + g) * STATE;
+#pragma unroll 1
+  for (int z = 0; z < 4; ++z) {
+    const StateView& src = z == 0 ? p.gWy : (z == 1 ? p.gWq : (z == 2 ? p.gWk : p.gwb));
+    const StateView& out = z == 0 ? r.oWy : (z == 1 ? r.oWq : (z == 2 ? r.oWk : r.owb));
+    const int count = z < 3 ? E * E : 4 * E;
+    float* dst = single ? out.mat(0, h) : part + z * E * E;
+    for (int i = tid * 4; i < count; i += P * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (single && r.accumulate) acc = *reinterpret_cast<const float4*>(dst + i);
+      for (int m = 0; m < members; ++m) add4g(acc, src.mat(n0 + m, h) + i);
+      *reinterpret_cast<float4*>(dst + i) = acc;
+    }
+  }
+  if (single) {
+    if (tid == 0) cnt[0] = 0u;
+    return;
+  }
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) s_last = atomicAdd(&cnt[r.ng], 1u) == (unsigned)(r.ng - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  const float* parts = r.part + (long long)h * r.ng * STATE;
+#pragma unroll 1
+  for (int z = 0; z < 4; ++z) {
+    const StateView& out = z == 0 ? r.oWy : (z == 1 ? r.oWq : (z == 2 ? r.oWk : r.owb));
+    const int count = z < 3 ? E * E : 4 * E;
+    float* dst = out.mat(0, h);
+    for (int i = tid * 4; i < count; i += P * 4) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (r.accumulate) acc = *reinterpret_cast<const float4*>(dst + i);
+      for (int g2 = 0; g2 < r.ng; ++g2) add4g(acc, parts + (long long)g2 * STATE + z * E * E + i);
+      *reinterpret_cast<float4*>(dst + i) = acc;
+    }
+  }
+  for (int i = tid; i <= r.ng; i += P) cnt[i] = 0u;
+}
 
 template <int E, int C, int R, int NRG>
 __device__ __forceinline__ void load_tile(const float* g, int rg, int cg, u64 (&W)[R / 2][C]) {
@@ -424,7 +503,9 @@ struct SrwmFwdColSmem {
   static constexpr int TOTAL = 2 * IN_BYTES + XF_BYTES + OUT_BYTES + WB_BYTES + DQ_BYTES + DONE_BYTES;
 };
 
-template <typename TIO, int E, int T, bool PK, int MINB, bool DPRE, int NRP, bool EXT = false>
+// RST: the in-loop episode resets (F_DONE) are compiled in; the layer-level form without resets keeps
+// the plain step loop (the reset path costs registers in a kernel that already spills at E = 64).
+template <typename TIO, int E, int T, bool PK, int MINB, bool DPRE, int NRP, bool EXT = false, bool RST = EXT>
 __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdParams p) {
   static_assert(E == 16 || E == 32 || E == 64, "column layout: one warp per block");
   static_assert(T <= 32, "reset flags of a chunk travel as one 32-bit mask");
@@ -466,7 +547,7 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
 
   const bool smx = EXT && (p.flags & F_INPUT_SOFTMAX);
   const bool has_base = EXT && (p.flags & F_BASE);
-  const bool has_done = EXT && (p.flags & F_DONE);
+  const bool has_done = EXT && RST && (p.flags & F_DONE);
 
   u64 W[RL2][CPL];
   float* gW = (warp == 0 ? p.Wy : (warp == 1 ? p.Wq : p.Wk)).mat(n, h);
@@ -555,7 +636,7 @@ __global__ void __launch_bounds__(96, MINB) srwm_fwd_col_kernel(const SrwmFwdPar
     #pragma unroll 1
 
     for (int t = 0; t < nt; ++t, par ^= 1) {
-      if constexpr (EXT) {
+      if constexpr (EXT && RST) {
         if ((dmask >> t) & 1u) {   // episode boundary: the shift goes back to zero
           load_state(gB, nullptr);
           if (warp == 0) {
@@ -1290,6 +1371,9 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd_kernel(const SrwmBwdParams p
         if (restore) gwb[i] = wbT[(i % 4) * E + i / 4] - (bb ? bb[i] : 0.f);
       }
     }
+  }
+  if constexpr (EXT) {
+    if (p.flags & F_REDUCE) reduce_epilogue<E, P>(p, n, h, tid);
   }
 }
 

@@ -491,6 +491,7 @@ __global__ void __launch_bounds__(P, MINB) srwm_bwd2_kernel(const SrwmBwdParams 
       if (restore) gwb[i] = wbr[u] - (bb ? bb[i] : 0.f);
     }
   }
+  if (p.flags & F_REDUCE) reduce_epilogue<E, P>(p, n, h, tid);
 }
 
 }  // namespace srwm

@@ -20,8 +20,8 @@ FLAG_NO_SAVE, FLAG_STATE_GRAD_IN, FLAG_RESTORE_STATE, FLAG_INPUT_SOFTMAX, FLAG_Z
 OP_SRWM_FWD, OP_SRWM_BWD, OP_DELTA_FWD, OP_DELTA_BWD, OP_SRWM_BWD_DET = 0, 1, 2, 3, 4
 ABI_VERSION = 2
 
-ERR_NULL, ERR_SHAPE, ERR_HEAD_DIM, ERR_DTYPE, ERR_ALIGN, ERR_VARIANT, ERR_CUDA, ERR_TOO_LARGE = (
-    -1, -2, -3, -4, -5, -6, -7, -8)
+ERR_NULL, ERR_SHAPE, ERR_HEAD_DIM, ERR_DTYPE, ERR_ALIGN, ERR_VARIANT, ERR_CUDA, ERR_TOO_LARGE, ERR_UNSUPPORTED = (
+    -1, -2, -3, -4, -5, -6, -7, -8, -9)
 
 
 class Seq(C.Structure):
@@ -58,6 +58,12 @@ class SrwmExt(C.Structure):
     _fields_ = [("base_W_y", State), ("base_W_q", State), ("base_W_k", State), ("base_w_b", State),
                 ("shift_W_y", State), ("shift_W_q", State), ("shift_W_k", State), ("shift_w_b", State),
                 ("done", C.c_void_p), ("done_stride_n", C.c_int64), ("done_stride_l", C.c_int64)]
+
+
+class SrwmReduce(C.Structure):
+    _fields_ = [("grad_base_W_y", State), ("grad_base_W_q", State), ("grad_base_W_k", State),
+                ("grad_base_w_b", State), ("accumulate", C.c_int32), ("reserved", C.c_int32),
+                ("scratch", C.c_void_p), ("scratch_bytes", C.c_int64)]
 
 
 class SrwmBwdDetArgs(C.Structure):
@@ -109,6 +115,9 @@ SYMBOLS = {
     "srwm_b200_srwm_backward": (C.c_int, [C.POINTER(SrwmBwdArgs), C.c_void_p]),
     "srwm_b200_srwm_layer_forward": (C.c_int, [C.POINTER(SrwmFwdArgs), C.POINTER(SrwmExt), C.c_void_p]),
     "srwm_b200_srwm_layer_backward": (C.c_int, [C.POINTER(SrwmBwdArgs), C.POINTER(SrwmExt), C.c_void_p]),
+    "srwm_b200_srwm_layer_backward_reduced": (C.c_int, [C.POINTER(SrwmBwdArgs), C.POINTER(SrwmExt),
+                                                        C.POINTER(SrwmReduce), C.c_void_p]),
+    "srwm_b200_srwm_reduce_scratch_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "srwm_b200_srwm_backward_detached": (C.c_int, [C.POINTER(SrwmBwdDetArgs), C.c_void_p]),
     "srwm_b200_delta_forward": (C.c_int, [C.POINTER(DeltaFwdArgs), C.c_void_p]),
     "srwm_b200_delta_backward": (C.c_int, [C.POINTER(DeltaBwdArgs), C.c_void_p]),

@@ -133,10 +133,28 @@ def srwm_layer_forward(x, base, shift=None, done=None, input_softmax=True, save=
     return out, shift_out, saved
 
 
-def srwm_layer_backward(x, saved, grad_out, base, shift_out, grad_shift_out=None, input_softmax=True):
+_reduce_scratch = {}     # (device index, stream) -> scratch tensor of the fused batch reduction
+
+
+def _scratch_for(dev, nbytes):
+    """Working memory of the fused batch reduction, kept per (device, stream): calls on one stream
+    are ordered, so they can share it; calls on different streams may overlap and must not."""
+    key = (dev.index, torch.cuda.current_stream(dev).cuda_stream)
+    t = _reduce_scratch.get(key)
+    if t is None or t.numel() < nbytes:
+        t = torch.zeros(max(nbytes, 1024), dtype=torch.uint8, device=dev)
+        _reduce_scratch[key] = t
+    return t
+
+
+def srwm_layer_backward(x, saved, grad_out, base, shift_out, grad_shift_out=None, input_softmax=True,
+                        reduce_into=None, accumulate=False):
     """Backpropagation through time for ``srwm_layer_forward`` (no ``done``).  shift_out: the
     forward's final shift (left unchanged).  Returns (grad_x, gW_y, gW_q, gW_k, gw_b) with the
-    state gradients per sample (dL/dW_0)."""
+    state gradients per sample (dL/dW_0).
+    ``reduce_into``: four dense fp32 tensors ``[1,H,E,.]`` (e.g. views into a flat all-reduce bucket)
+    that receive the batch sums of those gradients, formed inside the backward kernel
+    (``accumulate``: added to their contents)."""
     _require_cuda(x, grad_out)
     N, H, Ln, E = x.shape
     dt = _io_dtype(x)
@@ -171,8 +189,24 @@ def srwm_layer_backward(x, saved, grad_out, base, shift_out, grad_shift_out=None
     a.grad_x = _seq_desc(grad_x)
     a.grad_W_y, a.grad_W_q, a.grad_W_k, a.grad_w_b = (_state_desc(t) for t in gW)
     e = _ext(base)
+    if reduce_into is None:
+        with torch.cuda.device(dev):
+            L.check(L.load().srwm_b200_srwm_layer_backward(C.byref(a), C.byref(e), _stream(x)), "srwm_layer_backward")
+        return (grad_x, *gW)
+    for t, w in zip(reduce_into, (E, E, E, 4)):
+        assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() == H * E * w, \
+            "reduce_into: four dense fp32 tensors [1,H,E,E] x3, [1,H,E,4]"
+    r = L.SrwmReduce()
+    r.grad_base_W_y, r.grad_base_W_q, r.grad_base_W_k = (L.State(t.data_ptr(), 0, E * E) for t in reduce_into[:3])
+    r.grad_base_w_b = L.State(reduce_into[3].data_ptr(), 0, E * 4)
+    r.accumulate = 1 if accumulate else 0
     with torch.cuda.device(dev):
-        L.check(L.load().srwm_b200_srwm_layer_backward(C.byref(a), C.byref(e), _stream(x)), "srwm_layer_backward")
+        lib = L.load()
+        nbytes = int(lib.srwm_b200_srwm_reduce_scratch_bytes(N, H, E))
+        scratch = _scratch_for(dev, nbytes)
+        r.scratch, r.scratch_bytes = scratch.data_ptr(), scratch.numel()
+        L.check(lib.srwm_b200_srwm_layer_backward_reduced(C.byref(a), C.byref(e), C.byref(r), _stream(x)),
+                "srwm_layer_backward_reduced")
     return (grad_x, *gW)
 
 

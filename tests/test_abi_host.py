@@ -208,3 +208,20 @@ def test_outputs_follow_the_memory_order_of_the_input_view():
     assert o2.shape == (B_, H_, L_, 8) and o2.stride() == (H_ * 8, 8, B_ * H_ * 8, 1)
     c = torch.zeros(B_, H_, L_, d_)
     assert ops._like(c).is_contiguous() and ops._like(c, 4).is_contiguous()
+
+
+def test_layer_backward_rejects_reset_flags():
+    """A reverse-time backward cannot cross an in-kernel reset: `done` in the extension block of the
+    layer-level backward is an error, not silently ignored."""
+    lib = L.load()
+    a = L.SrwmBwdArgs()
+    a.N, a.H, a.L, a.E = 2, 2, 4, 16
+    for f in ("W_y", "W_q", "W_k", "w_b", "grad_W_y", "grad_W_q", "grad_W_k", "grad_w_b"):
+        setattr(a, f, L.State(0x1000, 0, 0))
+    for f in ("x", "q", "k", "beta", "y_diff", "q_diff", "k_diff", "beta_diff", "grad_out", "grad_x"):
+        setattr(a, f, L.Seq(0x1000, 0, 0, 64))
+    e = L.SrwmExt()
+    e.base_W_y = e.base_W_q = e.base_W_k = e.base_w_b = L.State(0x2000, 0, 0)
+    e.done = 0x3000
+    assert lib.srwm_b200_srwm_layer_backward(C.byref(a), C.byref(e), None) == L.ERR_UNSUPPORTED
+    assert b"not supported" in lib.srwm_b200_strerror(L.ERR_UNSUPPORTED)

@@ -600,3 +600,58 @@ def test_layer_call_at_scale_matches_plain_operator_composition():
         assert orc.rel_max(a.grad, b.grad) < 2e-2      # bf16 activations feed a sum over 80 x 300 steps
     for a, w, b in zip(sh1, W, b2):
         assert float((a.detach() - (w.detach() - b.detach())).abs().max()) < 5e-3 * std
+
+
+# ---------------------------------------------------------------------------------------
+# batch reduction fused into the backward (srwm_b200_srwm_layer_backward_reduced)
+# ---------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("E", [16, 32, 64])
+@pytest.mark.parametrize("N", [1, 5, 64, 65, 130])
+def test_fused_batch_reduction_matches_the_separate_one(E, N):
+    """The slow-weight gradients formed inside the backward kernel (last CTA of a group of samples
+    adds the group, last group of a head adds the groups) against the batch sum of the per-sample
+    gradients in float64; per-sample outputs unchanged; two calls in a row (the counters return to
+    zero), accumulation, and bitwise repeatability."""
+    from srwm_b200 import layer_ops as lo
+    d = torch.device("cuda", 0)
+    H, L_ = 3, 20
+    g = torch.Generator().manual_seed(100 + N + E)
+    x = torch.randn(N, H, L_, E, generator=g).to(d)
+    go = torch.randn(N, H, L_, E, generator=g).to(d)
+    std = E ** -0.5
+    base = [(torch.randn(1, H, E, w, generator=g) * std).to(d) for w in (E, E, E, 4)]
+    out, shift_out, saved = lo.srwm_layer_forward(x, base, None, None, True)
+    plain = lo.srwm_layer_backward(x, saved, go, base, shift_out, None, True)
+    want = [t.double().sum(0, keepdim=True) for t in plain[1:]]
+    dst = [torch.full((1, H, E, w), float("nan"), device=d) for w in (E, E, E, 4)]
+    res = lo.srwm_layer_backward(x, saved, go, base, shift_out, None, True, reduce_into=dst)
+    for a, b in zip(res, plain):
+        assert torch.equal(a, b)                       # grad_x and the per-sample gradients: same bits
+    for a, b in zip(dst, want):
+        assert orc.rel_max(a.cpu(), b.cpu()) < 1e-5
+    first = [t.clone() for t in dst]
+    lo.srwm_layer_backward(x, saved, go, base, shift_out, None, True, reduce_into=dst)
+    for a, b in zip(dst, first):
+        assert torch.equal(a, b)                       # second call: same bits (fixed summation order)
+    lo.srwm_layer_backward(x, saved, go, base, shift_out, None, True, reduce_into=dst, accumulate=True)
+    for a, b in zip(dst, want):
+        assert orc.rel_max(a.cpu(), 2 * b.cpu()) < 1e-5
+    torch.cuda.synchronize()
+
+
+def test_fused_batch_reduction_rejects_bad_scratch():
+    import ctypes as C
+    from srwm_b200 import _lib as L
+    lib = L.load()
+    assert lib.srwm_b200_srwm_reduce_scratch_bytes(130, 3, 64) > lib.srwm_b200_srwm_reduce_scratch_bytes(64, 3, 64) > 0
+    assert lib.srwm_b200_srwm_reduce_scratch_bytes(4, 3, 7) == 0
+    a = L.SrwmBwdArgs()
+    a.N, a.H, a.L, a.E = 4, 2, 8, 16
+    r = L.SrwmReduce()
+    assert lib.srwm_b200_srwm_layer_backward_reduced(C.byref(a), None, None, None) == L.ERR_NULL
+    assert lib.srwm_b200_srwm_layer_backward_reduced(C.byref(a), None, C.byref(r), None) == L.ERR_NULL   # no scratch
+    r.scratch, r.scratch_bytes = 256, 16
+    assert lib.srwm_b200_srwm_layer_backward_reduced(C.byref(a), None, C.byref(r), None) == L.ERR_TOO_LARGE
+    r.scratch = 264
+    assert lib.srwm_b200_srwm_layer_backward_reduced(C.byref(a), None, C.byref(r), None) == L.ERR_ALIGN
