@@ -208,6 +208,37 @@ int srwm_b200_srwm_layer_backward_reduced(const srwm_b200_srwm_bwd_args* args, c
                                           const srwm_b200_srwm_reduce* red, void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------
+ * srwm_b200_srwm_layer_backward_reduced for hosts that cannot allocate device memory.
+ * (No counterpart in the reference: its extensions take every buffer from PyTorch.)
+ *
+ * Who this is for: a host that was handed its buffers and has no allocator of its own to ask for
+ * a scratch block -- a C plug-in inside a process whose device memory belongs entirely to another
+ * runtime's pool, or a fixed-budget deployment that sizes all device memory at start-up -- and a
+ * latency-critical loop such as the agents' inference thread running beside the learner on one
+ * GPU, where a cudaMalloc in the call path would stall the other thread's work because it
+ * synchronises the device.
+ *
+ * Same arguments, same kernel and same results as the call above; `scratch` and `scratch_bytes`
+ * of the reduce block are ignored.  The working memory is a fixed array inside the library image
+ * of SRWM_B200_STATIC_SCRATCH_BYTES bytes (each GPU that loads the library holds it until the
+ * process exits).  The call makes no cudaMalloc / cudaFree and calls no allocating routine.
+ *   - Limit: srwm_b200_srwm_reduce_scratch_bytes(N, H, E) must not exceed the array; otherwise
+ *     SRWM_B200_ERR_TOO_LARGE is returned and nothing runs.  Any N <= 64 fits (counters only);
+ *     beyond that the need is about H * ceil(N/32) * (3E*E + 4E) * 4 bytes, e.g. N=128, H=16
+ *     fits for every supported E, N=1024, H=16, E=64 does not.
+ *   - First call on a device: it looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current) and keeps it.  Make that first call outside any stream capture.
+ *   - All calls share the one array per device and it keeps what the last call left in it (the
+ *     call clears the part that has to start at zero).  Calls that overlap on the GPU -- two
+ *     streams, or two host threads without ordering between their streams -- race on it and give
+ *     wrong sums; order them, or use the caller-scratch variant for one of them.
+ * ---------------------------------------------------------------------------------- */
+#define SRWM_B200_STATIC_SCRATCH_BYTES (4 * 1024 * 1024)
+int srwm_b200_srwm_layer_backward_reduced_static(const srwm_b200_srwm_bwd_args* args,
+                                                 const srwm_b200_srwm_ext* ext,
+                                                 const srwm_b200_srwm_reduce* red, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------
  * SRWM backward with the state DETACHED at every step: the gradient the reference's
  * reinforcement-learning learner computes, which calls the layer one step at a time and
  * detaches the state it carries (reinforcement_learning/torchbeast/layer.py:412-421 under

@@ -284,6 +284,60 @@ int srwm_b200_srwm_layer_backward_reduced(const srwm_b200_srwm_bwd_args* a, cons
   return layer_backward_impl(a, x, red, red->scratch, stream);
 }
 
+// ---------------------------------------------------------------------------------------
+// The same call for hosts that cannot allocate device memory.  Its working memory is this
+// array, which is part of the library image: every GPU that loads the library sets the
+// SRWM_B200_STATIC_SCRATCH_BYTES aside until the process exits, whether or not the entry point
+// is ever called.  In host code the array's name is only a handle for the runtime, not a
+// device address, so the address is looked up with cudaGetSymbolAddress -- once per device,
+// with that device current -- and that pointer is what the kernel receives.
+// ---------------------------------------------------------------------------------------
+static __device__ __align__(256) unsigned char g_static_reduce_scratch[SRWM_B200_STATIC_SCRATCH_BYTES];
+
+namespace {
+// Device address of the array on the current device; looked up on the first call per device and
+// remembered (the look-up allocates nothing, but it is a runtime call that should not fall inside
+// a stream capture, which is why the first call on a device should be made outside one).
+void* static_scratch_address(int* cuda_err) {
+  static void* cache[64] = {nullptr};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) { *cuda_err = (int)e; return nullptr; }
+  if (dev < 0 || dev >= 64) { *cuda_err = (int)cudaErrorInvalidDevice; return nullptr; }
+  void* ptr = __atomic_load_n(&cache[dev], __ATOMIC_ACQUIRE);
+  if (ptr) return ptr;
+  e = cudaGetSymbolAddress((void**)&ptr, g_static_reduce_scratch);
+  if (e != cudaSuccess || !ptr) {
+    *cuda_err = (int)(e != cudaSuccess ? e : cudaErrorInvalidSymbol);
+    (void)cudaGetLastError();
+    return nullptr;
+  }
+  __atomic_store_n(&cache[dev], ptr, __ATOMIC_RELEASE);
+  return ptr;
+}
+}  // namespace
+
+int srwm_b200_srwm_layer_backward_reduced_static(const srwm_b200_srwm_bwd_args* a, const srwm_b200_srwm_ext* x,
+                                                 const srwm_b200_srwm_reduce* red, void* stream) {
+  if (!a || !red) return SRWM_B200_ERR_NULL;
+  void* ptr = nullptr;
+  if (a->N > 0 && a->H > 0 && head_dim_ok(a->E)) {
+    // sizes first: a call that does not fit is refused before anything touches the device
+    if (reduce_scratch_bytes(a->N, a->H, a->E) > (size_t)SRWM_B200_STATIC_SCRATCH_BYTES) return SRWM_B200_ERR_TOO_LARGE;
+    int ce = 0;
+    ptr = static_scratch_address(&ce);
+    if (!ptr) {
+      g_last_cuda_error = ce;
+      return SRWM_B200_ERR_CUDA;
+    }
+  }
+  // red->scratch / scratch_bytes are not looked at.  The shared routine clears the counters at the head
+  // of the array on the caller's stream (cudaMemsetAsync) before the kernel runs: whatever the
+  // previous call left in the array is either cleared (counters) or overwritten before it is read
+  // (group partials).
+  return layer_backward_impl(a, x, red, ptr, stream);
+}
+
 namespace {
 int layer_backward_impl(const srwm_b200_srwm_bwd_args* a, const srwm_b200_srwm_ext* x,
                         const srwm_b200_srwm_reduce* red, void* scratch, void* stream) {

@@ -19,6 +19,7 @@ F32, BF16 = 0, 1
 FLAG_NO_SAVE, FLAG_STATE_GRAD_IN, FLAG_RESTORE_STATE, FLAG_INPUT_SOFTMAX, FLAG_ZERO_INIT = 1, 2, 4, 8, 16
 OP_SRWM_FWD, OP_SRWM_BWD, OP_DELTA_FWD, OP_DELTA_BWD, OP_SRWM_BWD_DET = 0, 1, 2, 3, 4
 ABI_VERSION = 2
+STATIC_SCRATCH_BYTES = 4 * 1024 * 1024   # SRWM_B200_STATIC_SCRATCH_BYTES
 
 ERR_NULL, ERR_SHAPE, ERR_HEAD_DIM, ERR_DTYPE, ERR_ALIGN, ERR_VARIANT, ERR_CUDA, ERR_TOO_LARGE, ERR_UNSUPPORTED = (
     -1, -2, -3, -4, -5, -6, -7, -8, -9)
@@ -117,6 +118,8 @@ SYMBOLS = {
     "srwm_b200_srwm_layer_backward": (C.c_int, [C.POINTER(SrwmBwdArgs), C.POINTER(SrwmExt), C.c_void_p]),
     "srwm_b200_srwm_layer_backward_reduced": (C.c_int, [C.POINTER(SrwmBwdArgs), C.POINTER(SrwmExt),
                                                         C.POINTER(SrwmReduce), C.c_void_p]),
+    "srwm_b200_srwm_layer_backward_reduced_static": (C.c_int, [C.POINTER(SrwmBwdArgs), C.POINTER(SrwmExt),
+                                                               C.POINTER(SrwmReduce), C.c_void_p]),
     "srwm_b200_srwm_reduce_scratch_bytes": (C.c_size_t, [C.c_int32, C.c_int32, C.c_int32]),
     "srwm_b200_srwm_backward_detached": (C.c_int, [C.POINTER(SrwmBwdDetArgs), C.c_void_p]),
     "srwm_b200_delta_forward": (C.c_int, [C.POINTER(DeltaFwdArgs), C.c_void_p]),
