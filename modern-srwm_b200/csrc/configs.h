@@ -71,13 +71,13 @@
 // Second formulation of the backward (srwm_bwd2.cuh): Z(E, id, P, R, T, MINB, OPT); always serves the
 // layer-level form as well
 #define SRWM_BWD2_CONFIGS(Z)             \
-  Z(64, 1, 128, 8, 16, 2, 0)             \
+  Z(64, 1, 128, 8, 16, 2, 4)             \
   SRWM_TUNING(                           \
   Z(32, 4, 64, 4, 16, 5, 0)              \
   Z(32, 5, 64, 4, 8, 6, 0)               \
-  Z(64, 5, 128, 8, 16, 2, 1)             \
-  Z(64, 6, 128, 8, 16, 2, 2)             \
-  Z(64, 7, 128, 8, 16, 2, 3))
+  Z(64, 5, 128, 8, 16, 2, 0)             \
+  Z(64, 6, 128, 8, 16, 2, 6)             \
+  Z(64, 7, 128, 8, 16, 2, 12))
 
 // Backward with the state detached at every step (W_y and its gradient only): X(E, id, P, R, T, PK, MINB)
 #define SRWM_BWD_DET_CONFIGS(X)          \
