@@ -55,6 +55,15 @@
   Y(64, 8, 16, false, 4, true, 2, 0)     \
   Y(64, 9, 16, true, 3, true, 2, 0))
 
+// One warp per sequence (srwm_fwd_warp.cuh, head sizes up to 32): V(E, id, T, MINB); serves the layer-level form too
+#define SRWM_FWD_WARP_CONFIGS(V)         \
+  SRWM_TUNING(                           \
+  V(8, 2, 16, 32)                        \
+  V(16, 5, 16, 24)                       \
+  V(32, 9, 16, 12)                       \
+  V(32, 10, 16, 16)                      \
+  V(32, 11, 8, 12))
+
 // ---- SRWM backward ------------------------------------------------------------------------------
 #define SRWM_BWD_CONFIGS(X)              \
   X(8, 1, 32, 2, 16, true, 8, 1)         \

@@ -63,6 +63,26 @@ int run_col(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, 
   return launch_kernel(srwm_fwd_col_kernel<TIO, E, T, PK, MINB, DPRE, NRP>, p, grid, 96, smem, s, &dev_mask, cuda_err);
 }
 
+template <int E, int V, int T, int MINB>
+int run_warp(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
+  if (p.flags & EXT_FLAGS) {
+    constexpr int smem = SrwmFwdWarpSmem<TIO, E, T, true>::TOTAL;
+    if (info) { info->P = 32; info->R = E * E / 32; info->T = T; info->smem = smem; info->id = V; }
+    if (describe_only) return 0;
+    if (p.flags & F_DONE) {
+      static unsigned long long dev_mask_rst = 0;
+      return launch_kernel(srwm_fwd_warp_kernel<TIO, E, T, MINB, true, true>, p, grid, 32, smem, s, &dev_mask_rst, cuda_err);
+    }
+    static unsigned long long dev_mask_ext = 0;
+    return launch_kernel(srwm_fwd_warp_kernel<TIO, E, T, MINB, true, false>, p, grid, 32, smem, s, &dev_mask_ext, cuda_err);
+  }
+  constexpr int smem = SrwmFwdWarpSmem<TIO, E, T, false>::TOTAL;
+  if (info) { info->P = 32; info->R = E * E / 32; info->T = T; info->smem = smem; info->id = V; }
+  if (describe_only) return 0;
+  static unsigned long long dev_mask = 0;
+  return launch_kernel(srwm_fwd_warp_kernel<TIO, E, T, MINB, false, false>, p, grid, 32, smem, s, &dev_mask, cuda_err);
+}
+
 }  // namespace
 
 #if SRWM_TIO_BF16
@@ -83,6 +103,10 @@ int dispatch_srwm_fwd_f32(
     return run_col<E_, V_, T_, PK_, MINB_, DPRE_, NRP_, LAYER_>(p, grid, s, info, describe_only, cuda_err);
   SRWM_FWD_COL_CONFIGS(Y)
 #undef Y
+#define V(E_, V_, T_, MINB_) \
+  if (E == E_ && variant == V_) return run_warp<E_, V_, T_, MINB_>(p, grid, s, info, describe_only, cuda_err);
+  SRWM_FWD_WARP_CONFIGS(V)
+#undef V
   return (E == 8 || E == 16 || E == 32 || E == 64) ? -6 : -3;
 }
 

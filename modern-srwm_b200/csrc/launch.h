@@ -4,6 +4,7 @@
 #include "delta.cuh"
 #include "srwm.cuh"
 #include "srwm_bwd2.cuh"
+#include "srwm_fwd_warp.cuh"
 
 namespace srwm {
 

@@ -133,7 +133,7 @@ def test_srwm_parity_lengths(E, L):
     _srwm_check(2, 3, L, E)
 
 
-@pytest.mark.parametrize("E", [16, 32, 64])
+@pytest.mark.parametrize("E", [8, 16, 32, 64])
 def test_srwm_parity_all_variants(E):
     for vf in range(_nvar(0, E)):
         _srwm_check(2, 2, 35, E, variant=(vf, 0))
