@@ -92,8 +92,18 @@ int dispatch_srwm_fwd_f32(
 #endif
     int E, int variant, const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only,
     int* cuda_err, int sms) {
-  (void)sms;
-  if (variant == 0) variant = 1;   // one configuration per head size serves every grid
+  // E = 32: one warp per sequence once the grid offers more than eight sequences per multiprocessor
+  // (fewer instructions per step, but a longer step for a lone sequence) -- unless its last wave of
+  // twelve sequences per multiprocessor would be mostly empty (2048 sequences on 148 multiprocessors
+  // are 1.15 waves: no gain over the column layout there)
+  if (variant == 0) {
+    variant = 1;
+    if (E == 32) {
+      const int n_sm = current_sms(sms, describe_only), slots = 12 * n_sm;
+      const int full = grid / slots, rest = grid - full * slots;
+      if (grid > 8 * n_sm && (rest == 0 || full >= 3 || rest * 20 >= slots * 13)) variant = 2;
+    }
+  }
 #define X(E_, V_, P_, R_, T_, PK_, MINB_, LAYER_) \
   if (E == E_ && variant == V_) return run<E_, V_, P_, R_, T_, PK_, MINB_, LAYER_>(p, grid, s, info, describe_only, cuda_err);
   SRWM_FWD_CONFIGS(X)

@@ -77,13 +77,14 @@ def _done_bytes(done, N, Ln):
     return (done != 0).view(torch.uint8)
 
 
-def srwm_layer_forward(x, base, shift=None, done=None, input_softmax=True, save=True, inplace_state=False):
+def srwm_layer_forward(x, base, shift=None, done=None, input_softmax=True, save=True, inplace_state=False,
+                       variant=0):
     """Forward.  x [N,H,L,E] (raw activations with ``input_softmax``), base = 4 slow-weight
     tensors [1,H,E,.] (or per sample [N,H,E,.]), shift = optional 4 tensors [N,H,E,.], done =
     optional [N,L].  Returns (out, shift_out (4 new tensors), saved or None).
     ``inplace_state``: write the new shift over the given one (inference only: every thread
     overwrites exactly the state elements it read at the start, but a backward would no longer
-    find its initial shift)."""
+    find its initial shift).  ``variant``: kernel configuration id (0 = the library chooses)."""
     _require_cuda(x, *base)
     N, H, Ln, E = x.shape
     shapes = [(E, E)] * 3 + [(E, 4)]
@@ -109,7 +110,7 @@ def srwm_layer_forward(x, base, shift=None, done=None, input_softmax=True, save=
     a.N, a.H, a.L, a.E = N, H, Ln, E
     a.io_dtype = dt
     a.flags = (0 if save else L.FLAG_NO_SAVE) | (L.FLAG_INPUT_SOFTMAX if input_softmax else 0)
-    a.variant = 0
+    a.variant = variant
     a.x = _seq_desc(xs)
     a.W_y, a.W_q, a.W_k, a.w_b = (_state_desc(t) for t in shift_out)
     a.out = _seq_desc(out)

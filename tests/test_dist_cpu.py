@@ -49,6 +49,18 @@ def _worker(rank, world, port, q):
         bucket.all_reduce()
         bucket.wait()
         ok = all(torch.allclose(bucket.view(i), t.sum(0), atol=1e-5) for i, t in enumerate(per_sample))
+        # the training step's pattern: asynchronous all-reduce, overlapped with other work, waited
+        # for before the bucket is written again
+        for step in range(2):
+            bucket.wait()
+            for i, t in enumerate(per_sample):
+                bucket.reduce_into(i, (step + 1) * t[lo:hi])
+            work = bucket.all_reduce(async_op=True)
+            ok = ok and work is not None
+            _ = torch.randn(64, 64) @ torch.randn(64, 64)      # "the next forward"
+        bucket.wait()
+        ok = ok and bucket.work is None
+        ok = ok and all(torch.allclose(bucket.view(i), 2 * t.sum(0), atol=1e-5) for i, t in enumerate(per_sample))
         q.put((rank, ok))
     finally:
         dist.destroy_process_group()

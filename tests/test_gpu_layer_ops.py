@@ -655,3 +655,37 @@ def test_fused_batch_reduction_rejects_bad_scratch():
     assert lib.srwm_b200_srwm_layer_backward_reduced(C.byref(a), None, C.byref(r), None) == L.ERR_TOO_LARGE
     r.scratch = 264
     assert lib.srwm_b200_srwm_layer_backward_reduced(C.byref(a), None, C.byref(r), None) == L.ERR_ALIGN
+
+
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("mode", ["plain", "softmax_shift", "softmax_shift_done"])
+def test_one_warp_forward_layer_level_form_matches_column_layout(mode, dt):
+    """At d_head 32 the library switches to the one-warp-per-sequence forward on large grids.  Its
+    layer-level form (input softmax, base + shift state, episode resets) is checked here on a small
+    grid by asking for that configuration explicitly, against the column-layout kernel (which the
+    tests above hold to the oracle): outputs, final shift and every saved tensor."""
+    from srwm_b200 import layer_ops as lo
+    d = torch.device("cuda", 0)
+    N, H, L_, E = 3, 2, 37, 32
+    g = torch.Generator().manual_seed(77)
+    x = torch.randn(N, H, L_, E, generator=g).to(d, dt)
+    std = E ** -0.5
+    base = [(torch.randn(1, H, E, w, generator=g) * std).to(d) for w in (E, E, E, 4)]
+    shift = done = None
+    smx = False
+    if mode != "plain":
+        smx = True
+        shift = [(0.1 * std * torch.randn(N, H, E, w, generator=g)).to(d) for w in (E, E, E, 4)]
+    if mode == "softmax_shift_done":
+        done = (torch.rand(N, L_, generator=g) < 0.2).to(d)
+    ref = lo.srwm_layer_forward(x, base, shift, done, smx, variant=1)
+    got = lo.srwm_layer_forward(x, base, shift, done, smx, variant=2)
+    tol = 8e-3 if dt == torch.bfloat16 else 1e-5
+    assert orc.rel_max(got[0].float().cpu(), ref[0].float().cpu()) < tol
+    for a, b in zip(got[1], ref[1]):
+        assert float((a - b).abs().max()) < 1e-5 * std
+    for a, b in zip(got[2], ref[2]):
+        assert orc.rel_max(a.cpu(), b.cpu()) < 1e-5
+    # without saving (inference): same output
+    got2 = lo.srwm_layer_forward(x, base, shift, done, smx, save=False, variant=2)
+    assert torch.equal(got2[0], got[0]) and got2[2] is None
