@@ -58,12 +58,13 @@
   Y(64, 8, 16, false, 4, true, 2, 0)     \
   Y(64, 9, 16, true, 3, true, 2, 0))
 
-// One warp per sequence (srwm_fwd_warp.cuh, head sizes up to 32): V(E, id, T, MINB); serves the layer-level form too
+// E lanes per sequence, 32 / E sequences per warp (srwm_fwd_warp.cuh, head sizes up to 32): V(E, id, T, MINB), T <= E;
+// serves the layer-level form too
 #define SRWM_FWD_WARP_CONFIGS(V)         \
   V(32, 2, 16, 12)                       \
   SRWM_TUNING(                           \
-  V(8, 2, 16, 32)                        \
-  V(16, 5, 16, 24)                       \
+  V(8, 2, 8, 24)                         \
+  V(16, 5, 16, 16)                       \
   V(32, 10, 8, 12))
 
 // ---- SRWM backward ------------------------------------------------------------------------------

@@ -65,22 +65,24 @@ int run_col(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, 
 
 template <int E, int V, int T, int MINB>
 int run_warp(const SrwmFwdParams& p, int grid, cudaStream_t s, KernelInfo* info, int describe_only, int* cuda_err) {
+  constexpr int SPW = 32 / E;                     // sequences per warp (= per CTA of 32 threads)
+  const int ctas = (grid + SPW - 1) / SPW;
   if (p.flags & EXT_FLAGS) {
-    constexpr int smem = SrwmFwdWarpSmem<TIO, E, T, true>::TOTAL;
-    if (info) { info->P = 32; info->R = E * E / 32; info->T = T; info->smem = smem; info->id = V; }
+    constexpr int smem = SPW * SrwmFwdWarpSmem<TIO, E, T, true>::TOTAL;
+    if (info) { info->P = E; info->R = E; info->T = T; info->smem = smem; info->id = V; }
     if (describe_only) return 0;
     if (p.flags & F_DONE) {
       static unsigned long long dev_mask_rst = 0;
-      return launch_kernel(srwm_fwd_warp_kernel<TIO, E, T, MINB, true, true>, p, grid, 32, smem, s, &dev_mask_rst, cuda_err);
+      return launch_kernel(srwm_fwd_warp_kernel<TIO, E, T, MINB, true, true>, p, ctas, 32, smem, s, &dev_mask_rst, cuda_err);
     }
     static unsigned long long dev_mask_ext = 0;
-    return launch_kernel(srwm_fwd_warp_kernel<TIO, E, T, MINB, true, false>, p, grid, 32, smem, s, &dev_mask_ext, cuda_err);
+    return launch_kernel(srwm_fwd_warp_kernel<TIO, E, T, MINB, true, false>, p, ctas, 32, smem, s, &dev_mask_ext, cuda_err);
   }
-  constexpr int smem = SrwmFwdWarpSmem<TIO, E, T, false>::TOTAL;
-  if (info) { info->P = 32; info->R = E * E / 32; info->T = T; info->smem = smem; info->id = V; }
+  constexpr int smem = SPW * SrwmFwdWarpSmem<TIO, E, T, false>::TOTAL;
+  if (info) { info->P = E; info->R = E; info->T = T; info->smem = smem; info->id = V; }
   if (describe_only) return 0;
   static unsigned long long dev_mask = 0;
-  return launch_kernel(srwm_fwd_warp_kernel<TIO, E, T, MINB, false, false>, p, grid, 32, smem, s, &dev_mask, cuda_err);
+  return launch_kernel(srwm_fwd_warp_kernel<TIO, E, T, MINB, false, false>, p, ctas, 32, smem, s, &dev_mask, cuda_err);
 }
 
 }  // namespace

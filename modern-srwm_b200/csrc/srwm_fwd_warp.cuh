@@ -3,12 +3,13 @@
 //
 // At these sizes a step has few FMAs (3 blocks x E x E x 3 passes) and the cost of the other
 // forward kernels is their fixed per-step overhead: three warps that each load the operand vectors,
-// a two-warp named barrier and a block-wide barrier per step.  Here one warp holds all of
-// [W_y | W_q | W_k | w_b]: lane (rp, c) holds column c of each of the three E x E blocks for the rows of
-// row part rp (32 / E row parts; whole columns at E = 32), so
+// a two-warp named barrier and a block-wide barrier per step.  Here E lanes hold all of
+// [W_y | W_q | W_k | w_b] of one sequence: lane c holds column c (all E rows) of each of the three E x E
+// blocks and row c of w_b; a warp serves 32 / E sequences side by side (one at E = 32, two at 16, four
+// at 8), every instruction working for all of them, so
 //   * an operand vector (x, q-k, k) is loaded once per step and feeds the three blocks,
-//   * q~ / k~ land one per lane (duplicated over the row parts): the softmax is a warp reduction
-//     (redux.sync max, shuffle-tree sum),
+//   * q~ / k~ land one per lane: the softmax is a reduction over the E lanes of the sequence
+//     (redux.sync max with the group's member mask, shuffle-tree sum),
 //   * q, k, q-k reach the other lanes through the output staging rows and a __syncwarp -- the kernel
 //     has no barrier at all inside the time loop,
 //   * row c of w_b lives in the lane that also holds k[c], so its rank-1 update is thread-local; its
@@ -32,36 +33,51 @@ struct SrwmFwdWarpSmem {
   static constexpr int TOTAL = 2 * IN_BYTES + XF_BYTES + OUT_BYTES + DQ_BYTES + DONE_BYTES;
 };
 
-// sum of v[0..4) over all 32 lanes, returned in every lane (a reduce-scatter over the two low lane
-// bits, three butterfly stages, four broadcasts: 10 shuffles instead of 20)
-__device__ __forceinline__ void allreduce4_warp(float (&v)[4], int lane) {
+// sum of v[0..4) over the E lanes of a sequence (E a power of two >= 8), returned in every one of them
+// (a reduce-scatter over the two low lane bits, log2(E) - 2 butterfly stages, four broadcasts)
+template <int E>
+__device__ __forceinline__ void allreduce4_group(float (&v)[4], int lane) {
   reduce_scatter<4, 4, 1>(v, lane);          // lane l holds the partial of value l % 4
   float s = v[0];
 #pragma unroll
-  for (int off = 4; off < 32; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  for (int off = 4; off < E; off <<= 1) s += __shfl_xor_sync(0xffffffffu, s, off);
+  const int g0 = lane & ~(E - 1);
 #pragma unroll
-  for (int j = 0; j < 4; ++j) v[j] = __shfl_sync(0xffffffffu, s, j);
+  for (int j = 0; j < 4; ++j) v[j] = __shfl_sync(0xffffffffu, s, g0 + j);
+}
+
+// max over the lanes named by `mask` (the E lanes of the caller's sequence)
+__device__ __forceinline__ float group_max(float v, unsigned mask) {
+  float r;
+  asm volatile("redux.sync.max.f32 %0, %1, %2;" : "=f"(r) : "f"(v), "r"(mask));
+  return r;
 }
 
 template <typename TIO, int E, int T, int MINB, bool EXT = false, bool RST = false>
 __global__ void __launch_bounds__(32, MINB) srwm_fwd_warp_kernel(const SrwmFwdParams p) {
   static_assert(E == 8 || E == 16 || E == 32, "one warp per sequence: head sizes up to 32");
-  static_assert(T <= 32, "reset flags of a chunk travel as one 32-bit mask");
   using SM = SrwmFwdWarpSmem<TIO, E, T, EXT>;
-  constexpr int P = 32;
-  constexpr int LPC = 32 / E;          // lanes per column = row parts
-  constexpr int RL = E / LPC;          // rows per lane
+  constexpr int P = E;                 // threads that serve one sequence
+  constexpr int SPW = 32 / E;          // sequences per warp
+  constexpr int RL = E;                // rows per lane: whole columns
   constexpr int RL2 = RL / 2;
   constexpr int NA = RL2 >= 4 ? 2 : 1;  // accumulator chains per block and pass
-  static_assert(RL % 2 == 0, "row pairs");
+  static_assert(T <= E, "reset flags of a chunk travel in the ballot bits of the sequence's lanes");
   const int lane = threadIdx.x;
-  const int c = lane % E, rp = lane / E;
-  const int r0 = rp * RL;              // first row of this lane's part
-  const int n = blockIdx.x / p.H, h = blockIdx.x % p.H;
-  const bool save = !(p.flags & F_NO_SAVE);
-  const bool owner = rp == 0;          // the lane that stores column c's results and holds row c of w_b
+  const int c = lane % E, sub = lane / E;
+  constexpr int r0 = 0;
+  const unsigned gmask = E == 32 ? 0xffffffffu : (((1u << (E % 32)) - 1u) << (sub * E));
+  // sequences beyond the grid (last warp of an odd grid) redo the last one and store nothing
+  const long long nseq = (long long)p.N * p.H;
+  const long long seq_raw = (long long)blockIdx.x * SPW + sub;
+  const bool active = seq_raw < nseq;
+  const long long seq = active ? seq_raw : nseq - 1;
+  const int n = (int)(seq / p.H), h = (int)(seq % p.H);
+  const bool save = !(p.flags & F_NO_SAVE) && active;
+  constexpr bool owner = true;         // every lane holds row c of w_b and stores column c's results
 
-  extern __shared__ __align__(16) unsigned char smem[];
+  extern __shared__ __align__(16) unsigned char smem_all[];
+  unsigned char* smem = smem_all + sub * SM::TOTAL;   // this sequence's staging area
   float* xf32 = reinterpret_cast<float*>(smem + 2 * SM::IN_BYTES);
   unsigned char* s_o = smem + 2 * SM::IN_BYTES + SM::XF_BYTES;
   TIO* sy = reinterpret_cast<TIO*>(s_o);
@@ -124,12 +140,12 @@ __global__ void __launch_bounds__(32, MINB) srwm_fwd_warp_kernel(const SrwmFwdPa
   auto stage_chunk = [&](int ch) {
     const int t0 = ch * T, nt = min(T, L - t0);
     if (SRWM_BAD_ROWS(p.dbg, 9, t0, nt, L, T)) return;
-    stage_rows<SM::ROW_IO, P>(in_buf(ch & 1), p.x.row(n, h, t0), p.x.sl, nt, lane);
+    stage_rows<SM::ROW_IO, P>(in_buf(ch & 1), p.x.row(n, h, t0), p.x.sl, nt, c);
   };
   stage_chunk(0);
   cp_async_commit();
   int dn_next = 0;
-  if (has_done && lane < min(T, L)) dn_next = p.done[(long long)n * p.done_sn + (long long)lane * p.done_sl];
+  if (has_done && c < min(T, L)) dn_next = p.done[(long long)n * p.done_sn + (long long)c * p.done_sl];
   const u64 zero2 = 0ull;
   int par = 0;
 
@@ -139,9 +155,9 @@ __global__ void __launch_bounds__(32, MINB) srwm_fwd_warp_kernel(const SrwmFwdPa
     if (ch + 1 < nchunks) stage_chunk(ch + 1);
     cp_async_commit();
     if (has_done) {
-      if (lane < T) sdone[lane] = (unsigned char)dn_next;
-      if (lane < min(T, L - t0 - T))
-        dn_next = p.done[(long long)n * p.done_sn + (long long)(t0 + T + lane) * p.done_sl];
+      if (c < T) sdone[c] = (unsigned char)dn_next;
+      if (c < min(T, L - t0 - T))
+        dn_next = p.done[(long long)n * p.done_sn + (long long)(t0 + T + c) * p.done_sl];
     }
     cp_async_wait<1>();
     __syncwarp();   // chunk ch staged; the output stage of the previous chunk has been flushed
@@ -149,17 +165,18 @@ __global__ void __launch_bounds__(32, MINB) srwm_fwd_warp_kernel(const SrwmFwdPa
     if constexpr (sizeof(TIO) == 4) {
       float* xs = reinterpret_cast<float*>(in_buf(ch & 1));
       if (smx) {
-        softmax_rows<TIO, E, P, T>(xs, xs, nt, lane);
+        softmax_rows<TIO, E, P, T>(xs, xs, nt, c);
         __syncwarp();
       }
       sxf = xs;
     } else {
-      if (smx) softmax_rows<TIO, E, P, T>(in_buf(ch & 1), xf32, nt, lane);
-      else convert_rows<TIO, E, P>(in_buf(ch & 1), xf32, nt, lane);
+      if (smx) softmax_rows<TIO, E, P, T>(in_buf(ch & 1), xf32, nt, c);
+      else convert_rows<TIO, E, P>(in_buf(ch & 1), xf32, nt, c);
       __syncwarp();
       sxf = xf32;
     }
-    const unsigned dmask = has_done ? __ballot_sync(0xffffffffu, lane < nt && sdone[lane] != 0) : 0u;
+    // reset flags of the chunk: bit t of the sequence's own lanes' ballot
+    const unsigned dmask = has_done ? ((__ballot_sync(0xffffffffu, c < nt && sdone[c] != 0) & gmask) >> (sub * E)) : 0u;
 
 #pragma unroll 1
     for (int t = 0; t < nt; ++t, par ^= 1) {
@@ -189,35 +206,29 @@ __global__ void __launch_bounds__(32, MINB) srwm_fwd_warp_kernel(const SrwmFwdPa
         }
         y = hsum2(ay[0]); qv = hsum2(aq[0]); kv = hsum2(ak[0]);
         if constexpr (NA == 2) { y += hsum2(ay[1]); qv += hsum2(aq[1]); kv += hsum2(ak[1]); }
-#pragma unroll
-        for (int off = E; off < 32; off <<= 1) {   // over the row parts: every lane of column c gets the sum
-          y += __shfl_xor_sync(0xffffffffu, y, off);
-          qv += __shfl_xor_sync(0xffffffffu, qv, off);
-          kv += __shfl_xor_sync(0xffffffffu, kv, off);
-        }
       }
       float beta[4];
       {
         const float xc = owner ? sxf[t * E + c] : 0.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) beta[j] = xc * wb[j];
-        allreduce4_warp(beta, lane);
+        allreduce4_group<E>(beta, lane);
 #pragma unroll
         for (int j = 0; j < 4; ++j) beta[j] = fast_sigmoid(beta[j]);
       }
-      // ---- softmax over the E columns (each value is present LPC times in the warp) --------------
+      // ---- softmax over the E columns of the sequence ----------------------------------------------
       {
-        const float mq = warp_max(qv), mk = warp_max(kv);
+        const float mq = group_max(qv, gmask), mk = group_max(kv, gmask);
         qv = __expf(qv - mq);
         kv = __expf(kv - mk);
         float sq_ = qv, sk_ = kv;
 #pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
+        for (int off = 1; off < E; off <<= 1) {
           sq_ += __shfl_xor_sync(0xffffffffu, sq_, off);
           sk_ += __shfl_xor_sync(0xffffffffu, sk_, off);
         }
-        qv *= __fdividef((float)LPC, sq_);
-        kv *= __fdividef((float)LPC, sk_);
+        qv *= __fdividef(1.f, sq_);
+        kv *= __fdividef(1.f, sk_);
       }
       if (owner) {
         from_f32(sy[t * E + c], y);
@@ -244,19 +255,13 @@ __global__ void __launch_bounds__(32, MINB) srwm_fwd_warp_kernel(const SrwmFwdPa
         }
         dy = hsum2(ay[0]); dqv = hsum2(aq[0]); dkv = hsum2(ak[0]);
         if constexpr (NA == 2) { dy += hsum2(ay[1]); dqv += hsum2(aq[1]); dkv += hsum2(ak[1]); }
-#pragma unroll
-        for (int off = E; off < 32; off <<= 1) {
-          dy += __shfl_xor_sync(0xffffffffu, dy, off);
-          dqv += __shfl_xor_sync(0xffffffffu, dqv, off);
-          dkv += __shfl_xor_sync(0xffffffffu, dkv, off);
-        }
       }
       float db[4];
       {
         const float dc = owner ? qv - kv : 0.f;
 #pragma unroll
         for (int j = 0; j < 4; ++j) db[j] = dc * wb[j];
-        allreduce4_warp(db, lane);
+        allreduce4_group<E>(db, lane);
       }
       if (save && owner) {
         syd[t * E + c] = dy;
@@ -285,15 +290,15 @@ __global__ void __launch_bounds__(32, MINB) srwm_fwd_warp_kernel(const SrwmFwdPa
     }
 
     __syncwarp();
-    flush_rows<SM::ROW_IO, P>(p.out.row(n, h, t0), p.out.sl, sy, nt, lane);
+    if (active) flush_rows<SM::ROW_IO, P>(p.out.row(n, h, t0), p.out.sl, sy, nt, c);
     if (save) {
-      flush_rows<SM::ROW_F, P>(p.q.row(n, h, t0), p.q.sl, sq, nt, lane);
-      flush_rows<SM::ROW_F, P>(p.k.row(n, h, t0), p.k.sl, sk, nt, lane);
-      flush_rows<SM::ROW_F, P>(p.yd.row(n, h, t0), p.yd.sl, syd, nt, lane);
-      flush_rows<SM::ROW_F, P>(p.qd.row(n, h, t0), p.qd.sl, sqd, nt, lane);
-      flush_rows<SM::ROW_F, P>(p.kd.row(n, h, t0), p.kd.sl, skd, nt, lane);
-      flush_rows<16, P>(p.beta.row(n, h, t0), p.beta.sl, sbeta, nt, lane);
-      flush_rows<16, P>(p.bd.row(n, h, t0), p.bd.sl, sbd, nt, lane);
+      flush_rows<SM::ROW_F, P>(p.q.row(n, h, t0), p.q.sl, sq, nt, c);
+      flush_rows<SM::ROW_F, P>(p.k.row(n, h, t0), p.k.sl, sk, nt, c);
+      flush_rows<SM::ROW_F, P>(p.yd.row(n, h, t0), p.yd.sl, syd, nt, c);
+      flush_rows<SM::ROW_F, P>(p.qd.row(n, h, t0), p.qd.sl, sqd, nt, c);
+      flush_rows<SM::ROW_F, P>(p.kd.row(n, h, t0), p.kd.sl, skd, nt, c);
+      flush_rows<16, P>(p.beta.row(n, h, t0), p.beta.sl, sbeta, nt, c);
+      flush_rows<16, P>(p.bd.row(n, h, t0), p.bd.sl, sbd, nt, c);
     }
   }
 
@@ -308,10 +313,11 @@ __global__ void __launch_bounds__(32, MINB) srwm_fwd_warp_kernel(const SrwmFwdPa
       g[(r0 + 2 * i2 + 1) * E + c] = b;
     }
   };
+  if (!active) return;
   store_col(gWy, has_base ? p.bWy.mat(n, h) : nullptr, Wy);
   store_col(gWq, has_base ? p.bWq.mat(n, h) : nullptr, Wq);
   store_col(gWk, has_base ? p.bWk.mat(n, h) : nullptr, Wk);
-  if (owner) {
+  {
     float4 v = make_float4(wb[0], wb[1], wb[2], wb[3]);
     if (has_base) {
       const float4 w = *reinterpret_cast<const float4*>(p.bwb.mat(n, h) + c * 4);

@@ -657,17 +657,33 @@ def test_fused_batch_reduction_rejects_bad_scratch():
     assert lib.srwm_b200_srwm_layer_backward_reduced(C.byref(a), None, C.byref(r), None) == L.ERR_ALIGN
 
 
+def _lanes_per_sequence_forward_id(E):
+    """Id of the forward configuration that gives a sequence E lanes of a warp (srwm_fwd_warp_kernel),
+    or None when this build of the library does not hold it for that head size."""
+    from srwm_b200 import _lib as L
+    for v in range(1, L.load().srwm_b200_num_variants(L.OP_SRWM_FWD, E)):
+        d = L.describe(L.OP_SRWM_FWD, E, variant=v)
+        if d["P"] == E and d["R"] == E:
+            return v
+    return None
+
+
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("mode", ["plain", "softmax_shift", "softmax_shift_done"])
-def test_one_warp_forward_layer_level_form_matches_column_layout(mode, dt):
-    """At d_head 32 the library switches to the one-warp-per-sequence forward on large grids.  Its
-    layer-level form (input softmax, base + shift state, episode resets) is checked here on a small
-    grid by asking for that configuration explicitly, against the column-layout kernel (which the
-    tests above hold to the oracle): outputs, final shift and every saved tensor."""
+@pytest.mark.parametrize("E,N", [(E_, N_) for E_, N_ in [(32, 3), (16, 3), (16, 4), (8, 5)]
+                                 if _lanes_per_sequence_forward_id(E_) is not None])   # head sizes this build holds it for
+def test_lanes_per_sequence_forward_layer_level_form(E, N, mode, dt):
+    """The forward that gives a sequence E lanes of a warp (one sequence per warp at d_head 32, two at 16,
+    four at 8; the library's choice at d_head 32 on large grids).  Its layer-level form (input softmax,
+    base + shift state, episode resets) is checked here on a small grid -- including sequence counts that
+    leave part of the last warp without a sequence -- by asking for that configuration explicitly, against
+    the default small-grid kernel (which the tests above hold to the oracle): outputs, final shift and
+    every saved tensor."""
     from srwm_b200 import layer_ops as lo
+    vid = _lanes_per_sequence_forward_id(E)
     d = torch.device("cuda", 0)
-    N, H, L_, E = 3, 2, 37, 32
-    g = torch.Generator().manual_seed(77)
+    H, L_ = 3, 37
+    g = torch.Generator().manual_seed(77 + E + N)
     x = torch.randn(N, H, L_, E, generator=g).to(d, dt)
     std = E ** -0.5
     base = [(torch.randn(1, H, E, w, generator=g) * std).to(d) for w in (E, E, E, 4)]
@@ -679,7 +695,7 @@ def test_one_warp_forward_layer_level_form_matches_column_layout(mode, dt):
     if mode == "softmax_shift_done":
         done = (torch.rand(N, L_, generator=g) < 0.2).to(d)
     ref = lo.srwm_layer_forward(x, base, shift, done, smx, variant=1)
-    got = lo.srwm_layer_forward(x, base, shift, done, smx, variant=2)
+    got = lo.srwm_layer_forward(x, base, shift, done, smx, variant=vid)
     tol = 8e-3 if dt == torch.bfloat16 else 1e-5
     assert orc.rel_max(got[0].float().cpu(), ref[0].float().cpu()) < tol
     for a, b in zip(got[1], ref[1]):
@@ -687,5 +703,5 @@ def test_one_warp_forward_layer_level_form_matches_column_layout(mode, dt):
     for a, b in zip(got[2], ref[2]):
         assert orc.rel_max(a.cpu(), b.cpu()) < 1e-5
     # without saving (inference): same output
-    got2 = lo.srwm_layer_forward(x, base, shift, done, smx, save=False, variant=2)
+    got2 = lo.srwm_layer_forward(x, base, shift, done, smx, save=False, variant=vid)
     assert torch.equal(got2[0], got[0]) and got2[2] is None
